@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the mixed NVFP4/MXFP8 linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[3], the one the headline metric is quoted on): prefill with
+M = 8192 tokens through the four Llama-3-8B linear shapes.  One step =
+    RMSNorm + Hadamard + pack of X[8192,4096]  -> fused mixed GEMM 4096 -> 6144   (QKV)
+    Hadamard + pack of X[8192,4096]            -> fused mixed GEMM 4096 -> 4096   (O)
+    RMSNorm + Hadamard + pack of X[8192,4096]  -> fused mixed GEMM 4096 -> 28672  (gate_up)
+    Hadamard + pack of X[8192,14336]           -> fused mixed GEMM 14336 -> 4096  (down)
+with K split 31/32 NVFP4 + 1/32 MXFP8, weights pre-packed once.  Inputs are synthetic
+(N(0,1) with 1% outlier channels x20, weights N(0,0.02)); the per-step working set (~1.1 GB)
+is far larger than the 126 MB L2, so no explicit flush is needed between iterations.
+
+`value` is GEMM+pack throughput with inputs resident in HBM; `e2e` is the same step driven
+from pinned host buffers (host->device copy of both activation matrices and device->host copy
+of the down-projection output inside the timed region).  With N > 1 every rank runs the same
+step on its own GPU (the per-op configurations do not shard: replicas only, weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's fake-quant path
+(oracle/plq_oracle.c, OpenMP, all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [("qkv", 4096, 6144, True), ("o", 4096, 4096, False), ("gate_up", 4096, 28672, True),
+          ("down", 14336, 4096, False)]   # name, K, N, fused RMSNorm on the input
+M_TOKENS = 8192
+NOMINAL_FP4_TFLOPS = 9000.0     # B200 dense FP4 (NVIDIA's sparse figure halved)
+NOMINAL_HBM_GBS = 8000.0
+
+
+def flops_of(m, shapes=SHAPES):
+    return sum(2.0 * m * n * k for _, k, n, _ in shapes)
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p["bf16_tflops_sustained"]), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except Exception:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        busy = [v for v in sm if mx and v > 0.5 * mx] or sm
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the CPU port of the reference's fake-quant path, bounded sample
+# ------------------------------------------------------------------------------------------------
+SAMPLE_M, SAMPLE_N = 256, 2048
+
+
+def run_cpu_sample(steps: int, warmup: int):
+    """Times [RMSNorm] + Hadamard + fake-quant pack of SAMPLE_M activation rows and the float32
+    product with SAMPLE_N pre-quantised weight rows, for each of the four shapes (full K)."""
+    import numpy as np
+    import torch
+    from oracle import cport
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    g = torch.Generator().manual_seed(1234)
+    work = []
+    for name, k, n, norm in SHAPES:
+        x = torch.randn(SAMPLE_M, k, generator=g)
+        x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
+        w = torch.randn(SAMPLE_N, k, generator=g) * 0.02
+        gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
+        pw = cport.prepare(bits(w.to(torch.bfloat16)), k // 32, hadamard=True)      # weight prep: once, untimed
+        wdq = cport.dequant(pw)
+        work.append((bits(x.to(torch.bfloat16)), bits(gamma) if norm else None, k, wdq))
+    import ctypes
+    lib = cport.lib()
+
+    def step():
+        for xb, gb, k, wdq in work:
+            px = cport.prepare(xb, k // 32, gb, 1e-6, True)
+            a = cport.dequant(px)
+            y = np.empty((SAMPLE_M, SAMPLE_N), np.float32)
+            lib.plqo_matmul_nt(a.ctypes.data_as(ctypes.c_void_p), wdq.ctypes.data_as(ctypes.c_void_p), SAMPLE_M,
+                               SAMPLE_N, k, y.ctypes.data_as(ctypes.c_void_p))
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    fl = sum(2.0 * SAMPLE_M * SAMPLE_N * k for _, k, _, _ in SHAPES)
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cport.num_threads(), "kind": "port",
+            "sample": f"{SAMPLE_M} token rows x {SAMPLE_N} weight rows of each of the 4 shapes, full K, "
+                      f"pack + float32 product, weight quantisation excluded", "ms_per_step": dt * 1e3}
+
+
+def config_dict(n_gpus):
+    return {"workload": "prefill M=8192 x Llama-3-8B linear shapes (4096->6144, 4096->4096, 4096->28672, "
+                        "14336->4096), K split 31/32 NVFP4 + 1/32 MXFP8, RMSNorm/Hadamard/pack on device",
+            "m_tokens": M_TOKENS, "l2": "per-step working set ~1.1 GB >> 126 MB L2, no flush needed",
+            "parallelism": f"replicas x{n_gpus}" if n_gpus > 1 else "single GPU"}
+
+
+def main_reference(args, rank):
+    if rank != 0:
+        return
+    steps = max(args.steps, 1)
+    b = run_cpu_sample(steps, min(args.warmup, 2))
+    line = {"impl": "reference", "metric": "mixed NVFP4/MXFP8 GEMM TFLOP/s", "value": b["value"], "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": b["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)",
+            "data": "synthetic", "config": config_dict(args.gpus),
+            "cpu_baseline": {k: b[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": b["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def main_ours(args, rank, local_rank, world):
+    import torch
+    import plaquant_b200 as plq
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: plaquant_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    plq.lib()
+    peaks = load_peaks()
+
+    # ---- synthetic data: host (pinned) masters and device copies ---------------------------------
+    g = torch.Generator().manual_seed(1000 * 3 + rank)
+    def activ(k):
+        x = torch.randn(M_TOKENS, k, generator=g, dtype=torch.float32)
+        x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
+        return x.to(torch.bfloat16).pin_memory()
+    x_host = {4096: activ(4096), 14336: activ(14336)}
+    x_dev = {k: torch.empty_like(v, device=dev) for k, v in x_host.items()}
+    for k in x_host:
+        x_dev[k].copy_(x_host[k])
+    layers = []
+    for name, k, n, norm in SHAPES:
+        w = (torch.randn(n, k, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(dev)
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="tiled")
+        gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16).to(dev) if norm else None
+        pa = plq.alloc_packed(M_TOKENS, k, k // 32, "tiled", dev)
+        y = torch.empty(M_TOKENS, n, dtype=torch.bfloat16, device=dev)
+        layers.append({"name": name, "k": k, "n": n, "pw": pw, "gamma": gamma, "pa": pa, "y": y})
+        del w
+    y_host = torch.empty(M_TOKENS, SHAPES[-1][2], dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+
+    gemm_events = []
+
+    def step(record=False):
+        for L in layers:
+            plq.pack(x_dev[L["k"]], L["k"] // 32, hadamard=True, gamma=L["gamma"], eps=1e-6, out=L["pa"])
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            plq.mixed_gemm(L["pa"], L["pw"], out=L["y"])
+            if record:
+                e1.record()
+                gemm_events.append((L["name"], e0, e1))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---- device-resident timing -------------------------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    plq.check_device_status()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    plq.check_device_status()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    per_gemm = {}
+    for name, a, b in gemm_events:
+        per_gemm.setdefault(name, []).append(a.elapsed_time(b))
+    gemm_ms = sum(sum(v) / len(v) for v in per_gemm.values())
+    fl = flops_of(M_TOKENS)
+    value = world * fl / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end from pinned host buffers ----------------------------------------------------------
+    def step_e2e():
+        for k in x_host:
+            x_dev[k].copy_(x_host[k], non_blocking=True)
+        step()
+        y_host.copy_(layers[-1]["y"], non_blocking=True)
+    for _ in range(min(args.warmup, 3)):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    h2d = sum(v.numel() * 2 for v in x_host.values())
+    d2h = y_host.numel() * 2
+
+    # ---- the other two kernels of the path, timed alone (rank 0 reports) -------------------------------
+    extra = {}
+    if rank == 0:
+        extra = side_benchmarks(plq, torch, dev, peaks)
+
+    if rank != 0:
+        return
+    gemm_tflops = fl / (gemm_ms * 1e-3) / 1e12
+    fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": "mixed NVFP4/MXFP8 GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)", "data": "synthetic",
+        "config": config_dict(world),
+        "e2e": {"value": world * fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+        "gpu_launches": 2 * len(layers) * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "mixed_gemm_kernel<256>", "achieved": gemm_tflops,
+                     "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
+                     "peak_source": f"4 x {peaks['source']} cuBLAS bf16 sustained ({peaks['bf16_tflops_sustained']} TF/s); "
+                                    "no FP4 peak is measured on this pool",
+                     "frac_of_nominal_fp4": gemm_tflops / NOMINAL_FP4_TFLOPS, "nominal_fp4_tflops": NOMINAL_FP4_TFLOPS,
+                     "flops_per_step": fl, "gemm_ms_per_step": gemm_ms,
+                     "per_gemm_ms": {k: sum(v) / len(v) for k, v in per_gemm.items()},
+                     "per_gemm_tflops": {L["name"]: 2.0 * M_TOKENS * L["n"] * L["k"] / (sum(per_gemm[L["name"]]) / len(per_gemm[L["name"]]) * 1e-3) / 1e12 for L in layers},
+                     "traffic": None},
+        **extra,
+    }
+    if world == 1:
+        try:
+            line["cpu_baseline"] = {k: v for k, v in run_cpu_sample(3, 1).items() if k != "ms_per_step"}
+        except Exception as exc:  # the checker library could not be built on this host
+            line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+    print(json.dumps(line), flush=True)
+
+
+def time_cuda(torch, fn, iters, flush=None):
+    """Average milliseconds of fn() over `iters` runs, each preceded by an L2 flush when given."""
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        tot += a.elapsed_time(b)
+    return tot / iters
+
+
+def side_benchmarks(plq, torch, dev, peaks):
+    """configs[1] (fused RMSNorm-quant + Hadamard-pack, [4096, 4096]) and configs[2] (decode GEMV
+    sweep), each kernel timed alone with an L2 flush before every launch; HBM roofline."""
+    flush = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)     # 256 MB > L2
+    out = {}
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(4096, 4096, generator=g)
+    x[:, torch.randperm(4096, generator=g)[:40]] *= 20.0
+    x = x.to(torch.bfloat16).to(dev)
+    gamma = (torch.rand(4096, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+    pa = plq.alloc_packed(4096, 4096, 128, "tiled", dev)
+    fn = lambda: plq.pack(x, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pa)
+    for _ in range(5):
+        fn()
+    ms = time_cuda(torch, fn, 20, flush)
+    nbytes = 2 * 4096 * 4096 + 2 * 4096 + 4096 * 2364
+    out["pack"] = {"workload": "RMSNorm + Hadamard128 + NVFP4/MXFP8 pack, bf16 [4096, 4096]", "us": ms * 1e3,
+                   "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                   "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                   "frac_of_nominal_hbm": nbytes / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
+    gv = {}
+    for name, k, n, _ in SHAPES:
+        w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
+        del w
+        for m in (1, 2, 4, 8):
+            xa = plq.pack(x[:m, :k] if k <= 4096 else torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev),
+                          k // 32, hadamard=True, sf_layout="rowmajor")
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            fn = lambda: plq.gemv(xa, pw, out=y)
+            for _ in range(3):
+                fn()
+            ms = time_cuda(torch, fn, 10, flush)
+            nb = pw.nbytes() + xa.nbytes() + m * n * 2
+            gv[f"{name}_m{m}"] = {"us": ms * 1e3, "bytes": nb, "gbs": nb / (ms * 1e-3) / 1e9,
+                                  "frac_of_measured_hbm": nb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                  "frac_of_nominal_hbm": nb / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
+        del pw
+    out["gemv"] = gv
+    out["hbm_peak_gbs"] = {"measured": peaks["hbm_gbs"], "nominal": NOMINAL_HBM_GBS, "source": peaks["source"]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        main_reference(args, rank)
+    else:
+        main_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,144 @@
+/*
+ * plq.h - C ABI of libplq_b200.so: the mixed NVFP4 / MXFP8 quantised-linear hot path on B200.
+ *
+ * Every entry point takes raw device pointers, 64-bit sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), launches
+ * asynchronously on that stream and returns an int status: 0 = ok, negative = argument or
+ * host-side error detected before anything was launched (see plq_status_string), positive
+ * values are only ever written by a kernel into the caller's status word.  The caller owns
+ * and allocates every buffer, outputs and workspaces included; the library never allocates,
+ * frees or keeps device memory.  There is no CPU fallback: on a device that is not sm_100
+ * the calls return PLQ_ERR_ARCH.
+ *
+ * Packed operand ("rows x K" matrix whose last K_hi columns are the outlier subspace):
+ *   lo_codes  u8 [rows, K_lo/2]   E2M1, two per byte, low nibble = lower K
+ *   lo_sf     u8                  E4M3 scale per 16 elements
+ *   hi_codes  u8 [rows, K_hi]     E4M3
+ *   hi_sf     u8                  E8M0 scale (exponent + 127) per 32 elements
+ * Scale buffers come in two layouts:
+ *   PLQ_SF_ROWMAJOR  [rows, K_lo/16] and [rows, K_hi/32]  (the reference spec's layout,
+ *                    docs/specs/spec-mxfp8-nvfp4.md:163-169)
+ *   PLQ_SF_TILED     512-byte chunks of 128 rows x 4 scales, byte (r%32)*16 + (r%128)/32*4
+ *                    + (k%4), chunks ordered K-fastest, rows and scales padded to 128 and 4:
+ *                    the order a block-scaled tcgen05.mma reads from tensor memory.
+ *                    Size in bytes: plq_sf_tiled_bytes(rows, n_scales_per_row).
+ * Constraints: K_lo % 64 == 0, K_hi % 32 == 0, K % 128 == 0 when a Hadamard rotation or
+ * RMSNorm is requested, K <= 32768; all pointers 16-byte aligned.
+ *
+ * Reference interfaces these replace are cited per function as path:line inside the
+ * reference project (Ther-LF/plaquant).
+ */
+#ifndef PLQ_H_
+#define PLQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define PLQ_API __attribute__((visibility("default")))
+#else
+#define PLQ_API
+#endif
+
+#define PLQ_OK              0
+#define PLQ_ERR_NULL       -1   /* a required pointer is NULL */
+#define PLQ_ERR_SHAPE      -2   /* a size violates the constraints above */
+#define PLQ_ERR_ALIGN      -3   /* a pointer is not 16-byte aligned */
+#define PLQ_ERR_ARCH       -4   /* current device is not compute capability 10.x */
+#define PLQ_ERR_CUDA       -5   /* a CUDA runtime call failed (plq_last_cuda_error) */
+#define PLQ_ERR_TENSORMAP  -6   /* cuTensorMapEncodeTiled rejected a descriptor */
+#define PLQ_ERR_LIMIT      -7   /* size beyond a documented maximum */
+#define PLQ_DEV_TIMEOUT     1   /* written by a kernel: a bounded wait ran out */
+
+#define PLQ_SF_ROWMAJOR 0
+#define PLQ_SF_TILED    1
+
+/* Library / ABI version (major * 100 + minor). */
+PLQ_API int plq_version(void);
+
+/* Human-readable text for a status value.  Never NULL. */
+PLQ_API const char* plq_status_string(int status);
+
+/* cudaError_t of the last failing runtime call on this thread (0 if none). */
+PLQ_API int plq_last_cuda_error(void);
+
+/* 0 if the current device can run the kernels (compute capability 10.x), else PLQ_ERR_ARCH. */
+PLQ_API int plq_device_check(void);
+
+/* Bytes of a PLQ_SF_TILED buffer for `rows` rows and `n_sf` scales per row. */
+PLQ_API int64_t plq_sf_tiled_bytes(int64_t rows, int64_t n_sf);
+
+/*
+ * Quantise-and-pack a bf16 matrix x[rows, k] (row stride k): optional block-Hadamard(128)
+ * rotation of every 128-column block (y = bf16((x.float() @ H128)/..)), then the last k_hi
+ * columns go to MXFP8 and the rest to NVFP4.
+ * Replaces, for activations: ActQuantizer.forward FP branch, promix/quantize/quant_utils.py:182-224
+ * (fake_quantize_nvfp4 :710-751, fake_quantize_mxfp8 :660-707) preceded by the online Hadamard
+ * of inference/quantize.py:447-448 / inference/forward_pass.py:283-284.
+ * For weights (x = W[N, K]): WeightQuantizer round-to-nearest, promix/quantize/kv_quant.py:161-166,
+ * after _apply_had_to_linear, promix/quantize/rotation.py:100-116.
+ */
+PLQ_API int plq_pack(const void* x_bf16, int64_t rows, int64_t k, int64_t k_hi, int hadamard,
+             void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout,
+             void* stream);
+
+/*
+ * Fused RMSNorm -> [block-Hadamard(128)] -> quantise-and-pack of hidden states x[rows, k]:
+ *   y = bf16(gamma * (x * rsqrt(mean(x^2) + eps))), float32 arithmetic,
+ * then as plq_pack.  Replaces rms_norm, inference/forward_pass.py:33-39, followed by the
+ * activation quantiser of the next linear (forward_pass.py:191-196, 264-268).
+ */
+PLQ_API int plq_rmsnorm_pack(const void* x_bf16, const void* gamma_bf16, float eps,
+                     int64_t rows, int64_t k, int64_t k_hi, int hadamard,
+                     void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout,
+                     void* stream);
+
+/*
+ * Dequantise a packed matrix back to bf16 [rows, k_lo + k_hi] (= the fake quantiser's return
+ * value, promix/quantize/quant_utils.py:750-751, :706-707).
+ */
+PLQ_API int plq_unpack(const void* lo_codes, const void* lo_sf, const void* hi_codes, const void* hi_sf,
+               int sf_layout, int64_t rows, int64_t k_lo, int64_t k_hi, void* y_bf16,
+               void* stream);
+
+/*
+ * Fused mixed GEMM: y[m, n] (bf16, row stride ldy elements) = deq(A)[m, :] . deq(B)[n, :]
+ * with A = packed activations (m rows), B = packed weights (n rows), both K-major, scale
+ * buffers in PLQ_SF_TILED layout.  One kernel, one tensor-memory accumulator: the NVFP4
+ * K-range runs as tcgen05.mma kind::mxf4nvf4 and the MXFP8 K-range as kind::mxf8f6f4 on top.
+ * `dev_status` is a device int32 the kernel sets to PLQ_DEV_TIMEOUT if a bounded wait ran
+ * out (the output is then undefined); it must be zero on entry and may not be NULL.
+ * Replaces the quantised linear itself, promix/quantize/quant_utils.py:389 /
+ * inference/forward_pass.py:319, in the two-K-phase call shape of fused_mixed_gemm,
+ * kernels/mixed_gemm/mixed_gemm.cu:346-350.
+ */
+PLQ_API int plq_mixed_gemm(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+                   const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+                   int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
+                   void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream);
+
+/*
+ * plq_mixed_gemm with the output tile width chosen by the caller (tile_n = 128 or 256) instead
+ * of by the built-in heuristic; used by tests and tuning.  Same reference counterpart.
+ */
+PLQ_API int plq_mixed_gemm_tile(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+                                const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+                                int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
+                                void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream, int tile_n);
+
+/*
+ * Decode GEMV, m <= 8: same contract as plq_mixed_gemm but streaming the weights once from
+ * HBM with 128-bit loads; scale buffers of both operands in PLQ_SF_ROWMAJOR layout.
+ */
+PLQ_API int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+             const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+             int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
+             void* y_bf16, int64_t ldy, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PLQ_H_ */

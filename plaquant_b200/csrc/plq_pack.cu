@@ -1,0 +1,332 @@
+// Quantise-and-pack kernels: [RMSNorm] -> [block-Hadamard 128] -> NVFP4 | MXFP8 codes + scales,
+// and the inverse (dequantise to bf16).  HBM-bound elementwise work, one CTA per row.
+//
+// Thread mapping.  A row is cut into 128-element blocks (the Hadamard block).  Four
+// consecutive lanes (a "quad", q = lane & 3) own one block; lane q holds the 32 elements
+// e = 32*j + 8*q + i (j = 0..3, i = 0..7), i.e. four 16-byte loads, so every 32-byte sector
+// fetched from HBM is consumed whole.  In this mapping
+//   * butterfly strides 1,2,4 (bits of i) and 32,64 (bits of j) stay inside a lane,
+//     strides 8,16 (bits of q) are two shuffle rounds inside the quad;
+//   * an NVFP4 block (16 elements) is one j of lanes {0,1} or {2,3}: one shuffle for the max;
+//   * an MXFP8 block (32 elements) is one j of the whole quad: two shuffles;
+//   * the NVFP4/MXFP8 boundary (a multiple of 64) never cuts a j group.
+// Summation and butterfly order are fixed and documented in the CPU oracle
+// (`_sumsq_det`, `block_hadamard_det`), which these kernels match bit for bit.
+#include "plq_quant.cuh"
+
+namespace plq {
+
+struct PackArgs {
+  const uint4* x;        // bf16 [rows, k]
+  const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
+  float eps;
+  float inv_k;           // unused (division is done exactly); kept for layout stability
+  int rows, k, k_lo;     // k_hi = k - k_lo
+  uint8_t* lo_codes;     // [rows, k_lo/2]
+  uint8_t* lo_sf;
+  uint8_t* hi_codes;     // [rows, k_hi]
+  uint8_t* hi_sf;
+  int sf_tiled;
+  int lo_chunks, hi_chunks;  // chunks per 128-row group in the tiled layouts
+};
+
+template <bool NORM, bool HAD>
+__global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int q = tid & 3;
+  const int k0 = (tid >> 2) * 128;                  // first element of this quad's block
+  const int lane = tid & 31;
+  float v[32];
+
+  // ---- load: four 16-byte pieces per lane ---------------------------------------------
+  const uint4* xrow = a.x + static_cast<size_t>(row) * (a.k >> 3);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int kk = k0 + 32 * j + 8 * q;
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (kk < a.k) w = __ldg(xrow + (kk >> 3));
+    v[8 * j + 0] = bf16lo_to_f32(w.x); v[8 * j + 1] = bf16hi_to_f32(w.x);
+    v[8 * j + 2] = bf16lo_to_f32(w.y); v[8 * j + 3] = bf16hi_to_f32(w.y);
+    v[8 * j + 4] = bf16lo_to_f32(w.z); v[8 * j + 5] = bf16hi_to_f32(w.z);
+    v[8 * j + 6] = bf16lo_to_f32(w.w); v[8 * j + 7] = bf16hi_to_f32(w.w);
+  }
+
+  // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
+  if constexpr (NORM) {
+    __shared__ float warp_sums[32];
+    float s = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) s = fmaf(v[e], v[e], s);     // v*v is exact for bf16 inputs
+    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 2);              // (p0+p1)+(p2+p3): block sum
+    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 8);
+    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 16);             // eight blocks, pairwise tree
+    if (lane == 0) warp_sums[tid >> 5] = s;
+    __syncthreads();
+    float tot = 0.0f;
+    const int nwarps = blockDim.x >> 5;
+    for (int w = 0; w < nwarps; ++w) tot = tot + warp_sums[w];  // left to right
+    const float var = __fdiv_rn(tot, static_cast<float>(a.k));
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kk = k0 + 32 * j + 8 * q;
+      uint4 g = make_uint4(0, 0, 0, 0);
+      if (kk < a.k) g = __ldg(a.gamma + (kk >> 3));
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float y0 = __fmul_rn(bf16lo_to_f32(gw[p]), __fmul_rn(v[8 * j + 2 * p], r));
+        const float y1 = __fmul_rn(bf16hi_to_f32(gw[p]), __fmul_rn(v[8 * j + 2 * p + 1], r));
+        const uint32_t b = f32x2_to_bf16x2(y0, y1);
+        v[8 * j + 2 * p] = bf16lo_to_f32(b);
+        v[8 * j + 2 * p + 1] = bf16hi_to_f32(b);
+      }
+    }
+  }
+
+  // ---- block-Hadamard(128): strides 1,2,4 | 8,16 (shuffles) | 32,64, then * 1/sqrt(128) ----
+  if constexpr (HAD) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        if ((e & h) == 0) {
+          const float x0 = v[e], x1 = v[e + h];
+          v[e] = __fadd_rn(x0, x1);
+          v[e + h] = __fsub_rn(x0, x1);
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 1; m <= 2; m <<= 1) {
+      const float sgn = (q & m) ? -1.0f : 1.0f;      // upper lane of the pair computes partner - own
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float o = __shfl_xor_sync(0xFFFFFFFFu, v[e], m);
+        v[e] = fmaf(sgn, v[e], o);                   // exact product, one rounding: own+other / other-own
+      }
+    }
+#pragma unroll
+    for (int h = 8; h < 32; h <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        if ((e & h) == 0) {
+          const float x0 = v[e], x1 = v[e + h];
+          v[e] = __fadd_rn(x0, x1);
+          v[e + h] = __fsub_rn(x0, x1);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      const uint32_t b = f32x2_to_bf16x2(__fmul_rn(v[e], 0.088388347648318441f),
+                                         __fmul_rn(v[e + 1], 0.088388347648318441f));
+      v[e] = bf16lo_to_f32(b);
+      v[e + 1] = bf16hi_to_f32(b);
+    }
+  }
+
+  // ---- quantise, 32 elements (one j group of the quad) at a time ---------------------------
+  uint32_t lo_sf_bytes = 0;                           // this lane pair's scale byte for j = 0..3
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int kg = k0 + 32 * j;                       // first element of the quad's j group
+    float x8[8];
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x8[i] = v[8 * j + i];
+      m = fmaxf(m, fabsf(x8[i]));
+    }
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    const float m32 = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    if (kg >= a.k) continue;
+    if (kg < a.k_lo) {
+      const uint32_t c = nvfp4_scale_code(m);
+      const float s = e4m3_code_to_f32(c);
+      const uint32_t codes = nvfp4_quantize8(x8, s, __frcp_rn(s));
+      *reinterpret_cast<uint32_t*>(a.lo_codes + (static_cast<size_t>(row) * a.k_lo + kg + 8 * q) / 2) = codes;
+      lo_sf_bytes |= c << (8 * j);
+    } else {
+      const uint32_t c = mxfp8_scale_code(m32);
+      const uint2 codes = mxfp8_quantize8(x8, __uint_as_float((254u - c) << 23));
+      const int kh = kg - a.k_lo;
+      *reinterpret_cast<uint2*>(a.hi_codes + static_cast<size_t>(row) * (a.k - a.k_lo) + kh + 8 * q) = codes;
+      if (q == 0) {
+        const int kb = kh >> 5;
+        const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.hi_chunks))
+                                      : static_cast<size_t>(row) * ((a.k - a.k_lo) >> 5) + kb;
+        a.hi_sf[off] = static_cast<uint8_t>(c);
+      }
+    }
+  }
+  // NVFP4 scales: lanes 0/1 of the quad hold blocks 0,2,4,6 (one byte per j), lanes 2/3 hold
+  // blocks 1,3,5,7.  Lane 0 interleaves them into two 4-byte words (64 elements each).
+  const uint32_t odd = __shfl_xor_sync(0xFFFFFFFFu, lo_sf_bytes, 2);
+  if (q == 0) {
+    const uint32_t w0 = __byte_perm(lo_sf_bytes, odd, 0x5140);   // blocks 0,1,2,3
+    const uint32_t w1 = __byte_perm(lo_sf_bytes, odd, 0x7362);   // blocks 4,5,6,7
+    const int kb = k0 >> 4;                                      // first 16-block index of this quad
+    if (a.sf_tiled) {
+      if (k0 < a.k_lo) *reinterpret_cast<uint32_t*>(a.lo_sf + sf_tiled_offset(row, kb, a.lo_chunks)) = w0;
+      if (k0 + 64 < a.k_lo) *reinterpret_cast<uint32_t*>(a.lo_sf + sf_tiled_offset(row, kb + 4, a.lo_chunks)) = w1;
+    } else {
+      uint8_t* p = a.lo_sf + static_cast<size_t>(row) * (a.k_lo >> 4) + kb;
+      if (k0 < a.k_lo) *reinterpret_cast<uint32_t*>(p) = w0;
+      if (k0 + 64 < a.k_lo) *reinterpret_cast<uint32_t*>(p + 4) = w1;
+    }
+  }
+}
+
+// ---- dequantise packed -> bf16 [rows, k]; one thread per 8 elements -------------------------
+struct UnpackArgs {
+  const uint8_t *lo_codes, *lo_sf, *hi_codes, *hi_sf;
+  int sf_tiled, rows, k_lo, k_hi, lo_chunks, hi_chunks;
+  uint4* y;
+};
+
+__global__ void unpack_kernel(const UnpackArgs a) {
+  const int k = a.k_lo + a.k_hi;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t per_row = k >> 3;
+  if (idx >= per_row * a.rows) return;
+  const int row = static_cast<int>(idx / per_row);
+  const int kk = static_cast<int>(idx % per_row) * 8;
+  float f[8];
+  if (kk < a.k_lo) {
+    const uint32_t codes = *reinterpret_cast<const uint32_t*>(a.lo_codes + (static_cast<size_t>(row) * a.k_lo + kk) / 2);
+    const int kb = kk >> 4;
+    const uint8_t sc = a.sf_tiled ? a.lo_sf[sf_tiled_offset(row, kb, a.lo_chunks)]
+                                  : a.lo_sf[static_cast<size_t>(row) * (a.k_lo >> 4) + kb];
+    const float s = e4m3_code_to_f32(sc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c = (codes >> (4 * i)) & 0xF;
+      const uint32_t mag = c & 7;
+      // E2M1 magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6
+      const float mv = mag < 2 ? 0.5f * mag : __uint_as_float(((mag >> 1) + 126u) << 23 | (mag & 1u) << 22);
+      f[i] = (c & 8) ? -(mv * s) : mv * s;
+    }
+  } else {
+    const int kh = kk - a.k_lo;
+    const uint2 codes = *reinterpret_cast<const uint2*>(a.hi_codes + static_cast<size_t>(row) * a.k_hi + kh);
+    const int kb = kh >> 5;
+    const uint8_t sc = a.sf_tiled ? a.hi_sf[sf_tiled_offset(row, kb, a.hi_chunks)]
+                                  : a.hi_sf[static_cast<size_t>(row) * (a.k_hi >> 5) + kb];
+    const float s = e8m0_to_f32(sc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c = ((i < 4 ? codes.x : codes.y) >> (8 * (i & 3))) & 0xFF;
+      const float mv = e4m3_code_to_f32(c & 0x7F);
+      f[i] = (c & 0x80) ? -(mv * s) : mv * s;
+    }
+  }
+  uint4 o;
+  o.x = f32x2_to_bf16x2(f[0], f[1]); o.y = f32x2_to_bf16x2(f[2], f[3]);
+  o.z = f32x2_to_bf16x2(f[4], f[5]); o.w = f32x2_to_bf16x2(f[6], f[7]);
+  a.y[idx] = o;
+}
+
+static int check_pack_args(const void* x, int64_t rows, int64_t k, int64_t k_hi, int hadamard, bool norm,
+                           void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout) {
+  if (rows < 0 || k <= 0 || k_hi < 0 || k_hi > k) return PLQ_ERR_SHAPE;
+  const int64_t k_lo = k - k_hi;
+  if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
+  if ((hadamard || norm) && k % 128 != 0) return PLQ_ERR_SHAPE;
+  if (k > 32768) return PLQ_ERR_LIMIT;
+  if (rows > 0x7FFFFFFF) return PLQ_ERR_LIMIT;
+  if (sf_layout != PLQ_SF_ROWMAJOR && sf_layout != PLQ_SF_TILED) return PLQ_ERR_SHAPE;
+  if (!x) return PLQ_ERR_NULL;
+  if (k_lo && (!lo_codes || !lo_sf)) return PLQ_ERR_NULL;
+  if (k_hi && (!hi_codes || !hi_sf)) return PLQ_ERR_NULL;
+  if (!aligned16(x) || !aligned16(lo_codes) || !aligned16(lo_sf) || !aligned16(hi_codes) || !aligned16(hi_sf))
+    return PLQ_ERR_ALIGN;
+  return PLQ_OK;
+}
+
+static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows, int64_t k, int64_t k_hi,
+                       int hadamard, void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout,
+                       void* stream) {
+  const bool norm = gamma != nullptr;
+  int st = check_pack_args(x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
+  if (st != PLQ_OK) return st;
+  if (norm && !aligned16(gamma)) return PLQ_ERR_ALIGN;
+  st = device_check();
+  if (st != PLQ_OK) return st;
+  if (rows == 0) return PLQ_OK;
+  PackArgs a;
+  a.x = static_cast<const uint4*>(x);
+  a.gamma = static_cast<const uint4*>(gamma);
+  a.eps = eps;
+  a.inv_k = 0.0f;
+  a.rows = static_cast<int>(rows);
+  a.k = static_cast<int>(k);
+  a.k_lo = static_cast<int>(k - k_hi);
+  a.lo_codes = static_cast<uint8_t*>(lo_codes);
+  a.lo_sf = static_cast<uint8_t*>(lo_sf);
+  a.hi_codes = static_cast<uint8_t*>(hi_codes);
+  a.hi_sf = static_cast<uint8_t*>(hi_sf);
+  a.sf_tiled = sf_layout == PLQ_SF_TILED;
+  a.lo_chunks = static_cast<int>(((k - k_hi) / 16 + 3) / 4);
+  a.hi_chunks = static_cast<int>((k_hi / 32 + 3) / 4);
+  const int blocks128 = static_cast<int>((k + 127) / 128);
+  const int threads = ((blocks128 * 4 + 31) / 32) * 32;
+  const dim3 grid(static_cast<unsigned>(rows));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (norm && hadamard) pack_kernel<true, true><<<grid, threads, 0, s>>>(a);
+  else if (norm) pack_kernel<true, false><<<grid, threads, 0, s>>>(a);
+  else if (hadamard) pack_kernel<false, true><<<grid, threads, 0, s>>>(a);
+  else pack_kernel<false, false><<<grid, threads, 0, s>>>(a);
+  PLQ_CUDA_TRY(cudaGetLastError());
+  return PLQ_OK;
+}
+
+}  // namespace plq
+
+extern "C" int plq_pack(const void* x_bf16, int64_t rows, int64_t k, int64_t k_hi, int hadamard, void* lo_codes,
+                        void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout, void* stream) {
+  return plq::launch_pack(x_bf16, nullptr, 0.0f, rows, k, k_hi, hadamard, lo_codes, lo_sf, hi_codes, hi_sf,
+                          sf_layout, stream);
+}
+
+extern "C" int plq_rmsnorm_pack(const void* x_bf16, const void* gamma_bf16, float eps, int64_t rows, int64_t k,
+                                int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf, void* hi_codes,
+                                void* hi_sf, int sf_layout, void* stream) {
+  if (!gamma_bf16) return PLQ_ERR_NULL;
+  return plq::launch_pack(x_bf16, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes, lo_sf, hi_codes, hi_sf,
+                          sf_layout, stream);
+}
+
+extern "C" int plq_unpack(const void* lo_codes, const void* lo_sf, const void* hi_codes, const void* hi_sf,
+                          int sf_layout, int64_t rows, int64_t k_lo, int64_t k_hi, void* y_bf16, void* stream) {
+  using namespace plq;
+  if (rows < 0 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0) return PLQ_ERR_SHAPE;
+  if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFF || k_lo + k_hi > (1 << 20)) return PLQ_ERR_LIMIT;
+  if (!y_bf16 || (k_lo && (!lo_codes || !lo_sf)) || (k_hi && (!hi_codes || !hi_sf))) return PLQ_ERR_NULL;
+  if (!aligned16(y_bf16) || !aligned16(lo_codes) || !aligned16(hi_codes)) return PLQ_ERR_ALIGN;
+  int st = device_check();
+  if (st != PLQ_OK) return st;
+  if (rows == 0) return PLQ_OK;
+  UnpackArgs a;
+  a.lo_codes = static_cast<const uint8_t*>(lo_codes);
+  a.lo_sf = static_cast<const uint8_t*>(lo_sf);
+  a.hi_codes = static_cast<const uint8_t*>(hi_codes);
+  a.hi_sf = static_cast<const uint8_t*>(hi_sf);
+  a.sf_tiled = sf_layout == PLQ_SF_TILED;
+  a.rows = static_cast<int>(rows);
+  a.k_lo = static_cast<int>(k_lo);
+  a.k_hi = static_cast<int>(k_hi);
+  a.lo_chunks = static_cast<int>((k_lo / 16 + 3) / 4);
+  a.hi_chunks = static_cast<int>((k_hi / 32 + 3) / 4);
+  a.y = static_cast<uint4*>(y_bf16);
+  const int64_t total = rows * ((k_lo + k_hi) / 8);
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  unpack_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  PLQ_CUDA_TRY(cudaGetLastError());
+  return PLQ_OK;
+}

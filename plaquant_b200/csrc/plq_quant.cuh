@@ -1,0 +1,121 @@
+// Device arithmetic of the NVFP4 / MXFP8 quantiser.
+//
+// Every function reproduces, bit for bit on bf16-valued inputs, what the reference's float32
+// fake quantiser computes (promix/quantize/quant_utils.py:660-751), but without its
+// 127-entry table scans and IEEE divisions:
+//   * NVFP4 scale:  smallest E4M3 value s with s >= fl(max/6).  For a bf16 max this is the
+//     smallest s with 6*s >= max (6*s is exact in float32 and a bf16 value can never sit
+//     within float32 rounding distance of 6*s without being equal to it), so a hardware
+//     round-to-nearest conversion plus one exact comparison finds it.
+//   * NVFP4 element: E2M1 code of fl(x/s).  x*fl(1/s) refined by one Newton step
+//     (two FMAs) equals m exactly whenever x == m*s for a rounding midpoint m, and is far
+//     (>= 2^-9 relative) from every midpoint otherwise, so the hardware RNE conversion of
+//     the refined quotient yields the same code as the reference's correctly rounded one.
+//   * MXFP8 scale: 2^e with the smallest e such that 448*2^e >= max, read off the bf16
+//     exponent and mantissa; element: x * 2^-e is exact, then hardware RNE to E4M3.
+//   * sign of zero: the reference multiplies the rounded magnitude by sign(x/s), so only a
+//     quotient that is strictly negative gets the sign bit.
+// The GPU parity tests sweep every (scale, bf16 value) pair against the CPU oracle.
+#pragma once
+
+#include "plq_common.cuh"
+
+namespace plq {
+#ifdef __CUDACC__
+
+// two bf16 in one 32-bit word -> float32 (element 0 in the low half)
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// round two float32 to bf16 (nearest even) and return them packed (a in the low half)
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2(float a, float b) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
+}
+
+// E4M3 code (0..0x7E) -> float32, subnormals included: the code shifted into the float32
+// exponent/mantissa position is the value scaled by 2^-120 (a float32 subnormal for codes < 8).
+__device__ __forceinline__ float e4m3_code_to_f32(uint32_t c) {
+  return __uint_as_float(c << 20) * 1.329227995784916e36f;  // 2^120
+}
+
+__device__ __forceinline__ uint32_t f32_to_e4m3_rn_sat(float v) {
+  uint16_t d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(0.0f), "f"(v));
+  return d & 0xFFu;
+}
+
+// NVFP4 block scale code from the block's absolute maximum (bf16-valued, >= 0, finite).
+__device__ __forceinline__ uint32_t nvfp4_scale_code(float bmax) {
+  uint32_t c = f32_to_e4m3_rn_sat(bmax * 0.16666667163372040f);
+  const float s = e4m3_code_to_f32(c);
+  if (6.0f * s < bmax) c += 1;       // nearest was one step short of the round-up
+  c = max(c, 1u);                    // floor 2^-9  (all-zero block -> code 0x01)
+  return min(c, 0x7Eu);              // saturate at 448, never the NaN code
+}
+
+// Eight float32 (bf16-valued) -> eight E2M1 codes, element 0 in bits [0,4).
+__device__ __forceinline__ uint32_t nvfp4_quantize8(const float (&x)[8], float s, float r) {
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float q0 = x[i] * r;
+    const float e = fmaf(-s, q0, x[i]);
+    q[i] = fmaf(e, r, q0);
+  }
+  uint32_t out;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(out)
+      : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+  // clear the sign nibble-bit of elements whose quotient is exactly zero (x == +-0)
+  uint32_t keep = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) keep |= (q[i] != 0.0f ? 0xFu : 0x7u) << (4 * i);
+  return out & keep;
+}
+
+// MXFP8 block scale byte (exponent + 127) from the block's absolute maximum (bf16-valued).
+__device__ __forceinline__ uint32_t mxfp8_scale_code(float bmax) {
+  const uint32_t u = __float_as_uint(bmax);
+  const int exp = static_cast<int>(u >> 23);          // biased; sign is 0
+  const int man = static_cast<int>((u >> 16) & 0x7F);  // the 7 bf16 mantissa bits
+  // max = (1 + man/128) * 2^(exp-127);  448 = 1.75 * 2^8  ->  e = exp-127-8 (+1 if 1+man/128 > 1.75)
+  int code = exp - 8 + (man > 96 ? 1 : 0);
+  if (exp == 0) code = 1;                              // zero / subnormal max
+  return static_cast<uint32_t>(max(code, 1));          // floor 2^-126
+}
+
+// Eight float32 -> eight E4M3 bytes (element 0 in the low byte of .x); inv = 2^-e.
+__device__ __forceinline__ uint2 mxfp8_quantize8(const float (&x)[8], float inv) {
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = x[i] * inv;
+  uint16_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[i]) : "f"(q[2 * i + 1]), "f"(q[2 * i]));
+  uint2 out;
+  out.x = static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16);
+  out.y = static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16);
+  uint32_t k0 = 0, k1 = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    k0 |= (q[i] != 0.0f ? 0xFFu : 0x7Fu) << (8 * i);
+    k1 |= (q[4 + i] != 0.0f ? 0xFFu : 0x7Fu) << (8 * i);
+  }
+  out.x &= k0;
+  out.y &= k1;
+  return out;
+}
+
+// 2^(code-127) as float32 for an E8M0 byte in [1, 254].
+__device__ __forceinline__ float e8m0_to_f32(uint32_t code) { return __uint_as_float(code << 23); }
+
+#endif  // __CUDACC__
+}  // namespace plq

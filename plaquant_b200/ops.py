@@ -1,0 +1,160 @@
+"""Torch-tensor front end of the C-ABI kernels.  PyTorch owns device memory and streams; all
+arithmetic happens in libplq_b200.so."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+SF_ROWMAJOR, SF_TILED = 0, 1
+_LAYOUTS = {"rowmajor": SF_ROWMAJOR, "tiled": SF_TILED, SF_ROWMAJOR: SF_ROWMAJOR, SF_TILED: SF_TILED}
+
+
+@dataclass
+class PackedMatrix:
+    """rows x (k_lo + k_hi) matrix in packed form (layout: include/plq.h)."""
+    rows: int
+    k_lo: int
+    k_hi: int
+    lo_codes: torch.Tensor   # u8 [rows, k_lo/2]
+    lo_sf: torch.Tensor      # u8, row-major [rows, k_lo/16] or tiled (flat)
+    hi_codes: torch.Tensor   # u8 [rows, k_hi]
+    hi_sf: torch.Tensor      # u8, row-major [rows, k_hi/32] or tiled (flat)
+    sf_layout: int
+
+    @property
+    def k(self) -> int:
+        return self.k_lo + self.k_hi
+
+    @property
+    def device(self):
+        return self.lo_codes.device
+
+    def nbytes(self) -> int:
+        return sum(t.numel() for t in (self.lo_codes, self.lo_sf, self.hi_codes, self.hi_sf))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: plaquant_b200 has no CPU path")
+
+
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the GEMM kernel writes PLQ_DEV_TIMEOUT into when a bounded wait runs out."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status_words[key]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronising read of the status word; raises PlqError if a kernel reported a timeout."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(dev)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        _lib.check(v)
+
+
+def alloc_packed(rows: int, k: int, k_hi: int, sf_layout, device) -> PackedMatrix:
+    layout = _LAYOUTS[sf_layout]
+    k_lo = k - k_hi
+    L = _lib.lib()
+    u8 = dict(dtype=torch.uint8, device=device)
+    if layout == SF_TILED:
+        lo_sf = torch.zeros(L.plq_sf_tiled_bytes(rows, k_lo // 16), **u8)
+        hi_sf = torch.zeros(L.plq_sf_tiled_bytes(rows, k_hi // 32), **u8)
+    else:
+        lo_sf = torch.empty(rows, k_lo // 16, **u8)
+        hi_sf = torch.empty(rows, k_hi // 32, **u8)
+    return PackedMatrix(rows, k_lo, k_hi, torch.empty(rows, k_lo // 2, **u8), lo_sf,
+                        torch.empty(rows, k_hi, **u8), hi_sf, layout)
+
+
+def pack(x: torch.Tensor, k_hi: int, hadamard: bool = False, sf_layout="tiled",
+         gamma: Optional[torch.Tensor] = None, eps: float = 1e-6,
+         out: Optional[PackedMatrix] = None) -> PackedMatrix:
+    """[RMSNorm(gamma, eps)] -> [block-Hadamard 128] -> NVFP4 | MXFP8 pack of bf16 x[..., K]."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("x must be bfloat16")
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    p = out if out is not None else alloc_packed(rows, k, k_hi, sf_layout, x.device)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        if gamma is None:
+            st = L.plq_pack(_ptr(x2), rows, k, k_hi, int(hadamard), _ptr(p.lo_codes), _ptr(p.lo_sf),
+                            _ptr(p.hi_codes), _ptr(p.hi_sf), p.sf_layout, _stream(x.device))
+        else:
+            _require_cuda(gamma, "gamma")
+            if gamma.dtype != torch.bfloat16 or gamma.numel() != k:
+                raise TypeError("gamma must be bfloat16 [K]")
+            st = L.plq_rmsnorm_pack(_ptr(x2), _ptr(gamma.contiguous()), float(eps), rows, k, k_hi, int(hadamard),
+                                    _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), p.sf_layout,
+                                    _stream(x.device))
+    _lib.check(st)
+    return p
+
+
+def unpack(p: PackedMatrix) -> torch.Tensor:
+    """Dequantise to bf16 [rows, K]: the value the reference's fake quantiser returns."""
+    y = torch.empty(p.rows, p.k, dtype=torch.bfloat16, device=p.device)
+    with torch.cuda.device(p.device):
+        st = _lib.lib().plq_unpack(_ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), p.sf_layout,
+                                   p.rows, p.k_lo, p.k_hi, _ptr(y), _stream(p.device))
+    _lib.check(st)
+    return y
+
+
+def _check_pair(a: PackedMatrix, b: PackedMatrix, layout: int) -> None:
+    if (a.k_lo, a.k_hi) != (b.k_lo, b.k_hi):
+        raise ValueError(f"K split mismatch: activations {a.k_lo}+{a.k_hi}, weights {b.k_lo}+{b.k_hi}")
+    if a.sf_layout != layout or b.sf_layout != layout:
+        raise ValueError("scale buffers are in the wrong layout for this kernel")
+
+
+def mixed_gemm(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
+               tile_n: Optional[int] = None) -> torch.Tensor:
+    """y[m, n] = deq(a) @ deq(b).T, bf16, via the fused tcgen05 kernel (tiled scale layout)."""
+    _check_pair(a, b, SF_TILED)
+    y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
+    L = _lib.lib()
+    args = [_ptr(a.lo_codes), _ptr(a.lo_sf), _ptr(a.hi_codes), _ptr(a.hi_sf),
+            _ptr(b.lo_codes), _ptr(b.lo_sf), _ptr(b.hi_codes), _ptr(b.hi_sf),
+            a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0), _ptr(status_word(a.device)), _stream(a.device)]
+    with torch.cuda.device(a.device):
+        st = L.plq_mixed_gemm(*args) if tile_n is None else L.plq_mixed_gemm_tile(*args, int(tile_n))
+    _lib.check(st)
+    return y
+
+
+def gemv(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode path, a.rows <= 8 (row-major scale layout)."""
+    _check_pair(a, b, SF_ROWMAJOR)
+    y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        st = _lib.lib().plq_gemv(_ptr(a.lo_codes), _ptr(a.lo_sf), _ptr(a.hi_codes), _ptr(a.hi_sf),
+                                 _ptr(b.lo_codes), _ptr(b.lo_sf), _ptr(b.hi_codes), _ptr(b.hi_sf),
+                                 a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0), _stream(a.device))
+    _lib.check(st)
+    return y

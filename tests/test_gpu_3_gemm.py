@@ -1,0 +1,144 @@
+"""Fused mixed GEMM (tcgen05, through the C ABI) against the CPU oracle's
+dequantise-then-float32-matmul.  Tolerance: rel-L2 <= 1e-3 measured in the output dtype (the
+oracle's float32 product is rounded to bf16 before comparing; bf16 rounding alone is 1.6e-3
+against an unrounded float32 product)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from tests._util import bits_of, f32_of, from_bits, packed_to_numpy, rel_l2, synth_activation, synth_weight
+
+pytestmark = pytest.mark.gpu
+plq = pytest.importorskip("plaquant_b200")
+
+TOL = 1e-3
+
+
+def _to_device(pd: dict, layout: str):
+    """oracle dict -> PackedMatrix on the GPU (used to feed hand-made codes to the kernel)."""
+    rows, k_lo, k_hi = pd["rows"], pd["k_lo"], pd["k_hi"]
+    lay = 1 if layout == "tiled" else 0
+    def sf(a, n):
+        if n == 0:
+            return torch.zeros(0, dtype=torch.uint8, device="cuda")
+        return torch.from_numpy(F.tile_sf(a) if lay else np.ascontiguousarray(a)).cuda()
+    return plq.PackedMatrix(rows, k_lo, k_hi, torch.from_numpy(pd["lo_codes"]).cuda().contiguous(),
+                            sf(pd["lo_sf"], k_lo // 16), torch.from_numpy(pd["hi_codes"]).cuda().contiguous(),
+                            sf(pd["hi_sf"], k_hi // 32), lay)
+
+
+def _oracle_bf16(pa: dict, pb: dict) -> np.ndarray:
+    return F.round_to_bf16(F.linear(pa, pb))
+
+
+def _run(pa_dev, pb_dev, tile_n):
+    y = plq.mixed_gemm(pa_dev, pb_dev, tile_n=tile_n)
+    plq.check_device_status()
+    return f32_of(y)
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_known_answer_all_ones(tile_n):
+    """Codes 1.0, scales 1.0: every output equals K.  Catches descriptor / pipeline errors."""
+    m, n, k_lo, k_hi = 128, 256, 512, 128
+    pa = {"rows": m, "k_lo": k_lo, "k_hi": k_hi, "lo_codes": np.full((m, k_lo // 2), 0x22, np.uint8),
+          "lo_sf": np.full((m, k_lo // 16), 0x38, np.uint8), "hi_codes": np.full((m, k_hi), 0x38, np.uint8),
+          "hi_sf": np.full((m, k_hi // 32), 127, np.uint8)}
+    pb = {**pa, "rows": n, "lo_codes": np.full((n, k_lo // 2), 0x22, np.uint8),
+          "lo_sf": np.full((n, k_lo // 16), 0x38, np.uint8), "hi_codes": np.full((n, k_hi), 0x38, np.uint8),
+          "hi_sf": np.full((n, k_hi // 32), 127, np.uint8)}
+    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), tile_n)
+    assert np.array_equal(y, np.full((m, n), float(k_lo + k_hi), np.float32))
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_known_answer_layout_probes(tile_n):
+    """Row-, column-, K- and scale-dependent patterns with exactly representable results, so any
+    permutation of rows, columns, K blocks, nibbles or scale bytes shows up as a wrong integer."""
+    rng = np.random.default_rng(5)
+    m, n, k_lo, k_hi = 256, 512, 768, 256
+    def mk(rows):
+        lo = rng.integers(0, 16, (rows, k_lo), dtype=np.uint8)
+        hi_mag = rng.integers(0x30, 0x48, (rows, k_hi), dtype=np.uint8)      # 0.5 .. 3.75
+        hi = hi_mag | (rng.integers(0, 2, (rows, k_hi), dtype=np.uint8) << 7)
+        return {"rows": rows, "k_lo": k_lo, "k_hi": k_hi, "lo_codes": F.pack_nibbles(lo),
+                "lo_sf": rng.integers(0x30, 0x41, (rows, k_lo // 16), dtype=np.uint8),   # 0.5 .. 2.0
+                "hi_codes": hi, "hi_sf": rng.integers(124, 131, (rows, k_hi // 32), dtype=np.uint8)}
+    pa, pb = mk(m), mk(n)
+    want = F.linear(pa, pb)
+    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), tile_n)
+    assert rel_l2(y, F.round_to_bf16(want)) <= TOL
+
+
+@pytest.mark.parametrize("m,n,k,k_hi", [
+    (128, 128, 256, 0), (128, 256, 256, 128), (7, 136, 192, 64), (129, 8, 64, 32), (300, 392, 1024, 448),
+    (64, 264, 128, 128), (16, 4096, 4096, 128), (130, 640, 14336, 448),
+])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_random_shapes_against_oracle(m, n, k, k_hi, tile_n):
+    x = synth_activation(m, k, seed=m + k)
+    w = synth_weight(n, k, seed=n + k + 1)
+    had = k % 128 == 0
+    pa = plq.pack(x.cuda(), k_hi, hadamard=had, sf_layout="tiled")
+    pb = plq.pack(w.cuda(), k_hi, hadamard=had, sf_layout="tiled")
+    y = _run(pa, pb, tile_n)
+    want = _oracle_bf16(packed_to_numpy(pa), packed_to_numpy(pb))
+    r = rel_l2(y, want)
+    assert r <= TOL, r
+
+
+def test_config0_single_linear_against_reference_fixture(golden_dir):
+    """X [16,4096] x W [4096,4096], block-Hadamard 128 on both, K = 3968 NVFP4 + 128 MXFP8;
+    compared with the reference's own fake-quant product (float32 matmul, rounded to bf16)."""
+    g = np.load(os.path.join(golden_dir, "linear_cfg0.npz"))
+    w = synth_weight(4096, 4096, seed=1)
+    assert int(bits_of(w).astype(np.uint64).sum()) == int(g["w_checksum"])
+    pa = plq.pack(from_bits(g["x"]), 128, hadamard=True, sf_layout="tiled")
+    pb = plq.pack(w.cuda(), 128, hadamard=True, sf_layout="tiled")
+    y = f32_of(plq.mixed_gemm(pa, pb))
+    plq.check_device_status()
+    ref = F.round_to_bf16(g["y_f32"])
+    r = rel_l2(y, ref)
+    # the rotation's float32 summation order differs from torch's (a bf16 ulp on ~1e-3 of the
+    # rotated inputs), which moves a few codes: allow that on top of the kernel tolerance
+    assert r <= 3e-3, r
+    # with the reference's own rotated activations the input-side slack disappears
+    pa2 = plq.pack(from_bits(g["xr"]), 128, hadamard=False, sf_layout="tiled")
+    want = _oracle_bf16(packed_to_numpy(pa2), packed_to_numpy(pb))
+    assert rel_l2(f32_of(plq.mixed_gemm(pa2, pb)), want) <= TOL
+
+
+def test_prefill_full_size_properties():
+    """M = 8192 on the QKV shape (4096 -> 6144): sampled rows against the oracle, identical rows
+    whatever the M they are computed in (tiles are independent), determinism, clean status."""
+    m, n, k, k_hi = 8192, 6144, 4096, 128
+    x = synth_activation(m, k, seed=3000)
+    w = synth_weight(n, k, seed=3001)
+    pa = plq.pack(x.cuda(), k_hi, hadamard=True, sf_layout="tiled")
+    pb = plq.pack(w.cuda(), k_hi, hadamard=True, sf_layout="tiled")
+    y1 = plq.mixed_gemm(pa, pb)
+    y2 = plq.mixed_gemm(pa, pb)
+    plq.check_device_status()
+    assert torch.equal(y1, y2)
+    sel = np.sort(np.random.default_rng(1).choice(m, 24, replace=False))
+    na, nb = packed_to_numpy(pa), packed_to_numpy(pb)
+    sub = {**na, "rows": len(sel), **{key: na[key][sel] for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf")}}
+    want = _oracle_bf16(sub, nb)
+    assert rel_l2(f32_of(y1)[sel], want) <= TOL
+    ps = plq.pack(x[:256].cuda(), k_hi, hadamard=True, sf_layout="tiled")
+    assert torch.equal(plq.mixed_gemm(ps, pb), y1[:256])
+
+
+def test_argument_errors():
+    x = synth_activation(16, 256, seed=1).cuda()
+    pa = plq.pack(x, 64, sf_layout="tiled")
+    pb = plq.pack(x, 64, sf_layout="rowmajor")
+    with pytest.raises(ValueError):
+        plq.mixed_gemm(pa, pb)                      # weights in the wrong scale layout
+    pb = plq.pack(x[:12], 64, sf_layout="tiled")     # N = 12 is not a multiple of 8
+    with pytest.raises(plq.PlqError) as e:
+        plq.mixed_gemm(pa, pb)
+    assert e.value.status == -2
