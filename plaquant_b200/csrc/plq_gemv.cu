@@ -37,11 +37,15 @@ constexpr int kGemvThreads = 256;
 constexpr int kGemvRowsPerCta = 128;
 constexpr int kGemvUnroll = 4;
 
-__device__ __forceinline__ void cvt_e2m1x4_to_f16x2(uint32_t half16, uint32_t& d0, uint32_t& d1) {
-  asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %2;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %0, lo;\n\tcvt.rn.f16x2.e2m1x2 %1, hi;\n\t}"
-      : "=r"(d0), "=r"(d1)
-      : "h"(static_cast<uint16_t>(half16)));
+// Eight E2M1 codes (one 32-bit word, element 0 in bits [0,4)) -> four f16x2 registers:
+// d0 = elements (0,1), d1 = (2,3), d2 = (4,5), d3 = (6,7).
+__device__ __forceinline__ void cvt_e2m1x8_to_f16x2(uint32_t w, uint32_t& d0, uint32_t& d1, uint32_t& d2,
+                                                    uint32_t& d3) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+      : "r"(w));
 }
 __device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint32_t half16) {
   uint32_t d;
@@ -94,8 +98,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
         const uint32_t codes = *reinterpret_cast<const uint32_t*>(a.a_lo + (static_cast<size_t>(row) * a.k_lo + k) / 2);
         const uint32_t sc = a.a_lo_sf[static_cast<size_t>(row) * (a.k_lo >> 4) + (k >> 4)];
         uint32_t s2 = cvt_e4m3x2_to_f16x2(sc | (sc << 8));
-        cvt_e2m1x4_to_f16x2(codes & 0xFFFF, o.x, o.y);
-        cvt_e2m1x4_to_f16x2(codes >> 16, o.z, o.w);
+        cvt_e2m1x8_to_f16x2(codes, o.x, o.y, o.z, o.w);
         o.x = hmul2_u32(o.x, s2); o.y = hmul2_u32(o.y, s2);
         o.z = hmul2_u32(o.z, s2); o.w = hmul2_u32(o.w, s2);
       }
@@ -160,15 +163,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
       for (int jj = 0; jj < 4; ++jj) {
         const uint4 xb = xrow[jj * 32];
         const uint32_t scale_a = jj < 2 ? sa0 : sa1, scale_b = jj < 2 ? sb0 : sb1;
-        uint32_t a0, a1, a2, a3;
-        cvt_e2m1x4_to_f16x2(wva[jj] & 0xFFFF, a0, a2);
-        cvt_e2m1x4_to_f16x2(wvb[jj] & 0xFFFF, a1, a3);
+        uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+        cvt_e2m1x8_to_f16x2(wva[jj], a0, a2, e0, e2);
+        cvt_e2m1x8_to_f16x2(wvb[jj], a1, a3, e1, e3);
         mma_16816(acc, hmul2_u32(a0, scale_a), hmul2_u32(a1, scale_b), hmul2_u32(a2, scale_a),
                   hmul2_u32(a3, scale_b), xb.x, xb.y);
-        cvt_e2m1x4_to_f16x2(wva[jj] >> 16, a0, a2);
-        cvt_e2m1x4_to_f16x2(wvb[jj] >> 16, a1, a3);
-        mma_16816(acc, hmul2_u32(a0, scale_a), hmul2_u32(a1, scale_b), hmul2_u32(a2, scale_a),
-                  hmul2_u32(a3, scale_b), xb.z, xb.w);
+        mma_16816(acc, hmul2_u32(e0, scale_a), hmul2_u32(e1, scale_b), hmul2_u32(e2, scale_a),
+                  hmul2_u32(e3, scale_b), xb.z, xb.w);
       }
     }
   }

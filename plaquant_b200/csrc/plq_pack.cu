@@ -239,6 +239,7 @@ static int check_pack_args(const void* x, int64_t rows, int64_t k, int64_t k_hi,
   if (k > 32768) return PLQ_ERR_LIMIT;
   if (rows > 0x7FFFFFFF) return PLQ_ERR_LIMIT;
   if (sf_layout != PLQ_SF_ROWMAJOR && sf_layout != PLQ_SF_TILED) return PLQ_ERR_SHAPE;
+  if (rows == 0) return PLQ_OK;   // nothing to read or write: pointers may be anything
   if (!x) return PLQ_ERR_NULL;
   if (k_lo && (!lo_codes || !lo_sf)) return PLQ_ERR_NULL;
   if (k_hi && (!hi_codes || !hi_sf)) return PLQ_ERR_NULL;
@@ -253,10 +254,10 @@ static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows
   const bool norm = gamma != nullptr;
   int st = check_pack_args(x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
   if (st != PLQ_OK) return st;
+  if (rows == 0) return PLQ_OK;
   if (norm && !aligned16(gamma)) return PLQ_ERR_ALIGN;
   st = device_check();
   if (st != PLQ_OK) return st;
-  if (rows == 0) return PLQ_OK;
   PackArgs a;
   a.x = static_cast<const uint4*>(x);
   a.gamma = static_cast<const uint4*>(gamma);

@@ -74,7 +74,7 @@ def test_known_answer_layout_probes(tile_n):
 
 
 @pytest.mark.parametrize("m,n,k,k_hi", [
-    (128, 128, 256, 0), (128, 256, 256, 128), (7, 136, 192, 64), (129, 8, 64, 32), (300, 392, 1024, 448),
+    (128, 128, 256, 0), (128, 256, 256, 128), (7, 136, 192, 64), (129, 8, 128, 64), (300, 392, 1024, 448),
     (64, 264, 128, 128), (16, 4096, 4096, 128), (130, 640, 14336, 448),
 ])
 @pytest.mark.parametrize("tile_n", [128, 256])
