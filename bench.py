@@ -367,8 +367,57 @@ def side_benchmarks(plq, torch, dev, peaks):
     return out
 
 
+def main_case(args):
+    """One kernel of the path on one fixed case, `warmup` + `steps` launches: the command the
+    ncu captures under profiles/ were taken from (small enough for a multi-pass capture)."""
+    import torch
+    import plaquant_b200 as plq
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(5)
+    def activ(m, k):
+        x = torch.randn(m, k, generator=g)
+        x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
+        return x.to(torch.bfloat16).to(dev)
+    name, k, n, _ = next(s for s in SHAPES if s[0] == args.shape)
+    if args.case == "pack":
+        x = activ(4096, 4096)
+        gamma = (torch.rand(4096, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+        pa = plq.alloc_packed(4096, 4096, 128, "tiled", dev)
+        fn = lambda: plq.pack(x, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pa)
+        work, unit = 2 * 4096 * 4096 + 2 * 4096 + 4096 * 2364, "GB/s"
+    elif args.case == "gemv":
+        w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
+        pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout="rowmajor")
+        y = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: plq.gemv(pa, pw, out=y)
+        work, unit = pw.nbytes() + pa.nbytes() + y.numel() * 2, "GB/s"
+    else:
+        w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="tiled")
+        pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout="tiled")
+        y = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: plq.mixed_gemm(pa, pw, out=y, variant=args.variant)
+        work, unit = 2.0 * args.m * n * k, "TFLOP/s"
+    flush = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    ms = time_cuda(torch, fn, args.steps, flush)
+    plq.check_device_status()
+    rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    print(json.dumps({"case": args.case, "shape": name, "m": args.m, "us_per_launch": ms * 1e3, "rate": rate,
+                      "unit": unit, "work": work}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, choices=["pack", "gemv", "gemm"],
+                    help="run one kernel on one fixed case instead of the full step")
+    ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
+    ap.add_argument("--m", type=int, default=None)
+    ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256", "128x256-st", "pair256x256-st"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -377,6 +426,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.case is not None:
+        if args.m is None:
+            args.m = 8 if args.case == "gemv" else M_TOKENS
+        return main_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         main_reference(args, rank)

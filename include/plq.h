@@ -121,13 +121,17 @@ PLQ_API int plq_mixed_gemm(const void* a_lo_codes, const void* a_lo_sf, const vo
                    void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream);
 
 /*
- * plq_mixed_gemm with the output tile width chosen by the caller (tile_n = 128 or 256) instead
- * of by the built-in heuristic; used by tests and tuning.  Same reference counterpart.
+ * plq_mixed_gemm with the tile shape chosen by the caller instead of by the built-in heuristic
+ * (tests and tuning).  Same reference counterpart.
  */
-PLQ_API int plq_mixed_gemm_tile(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
-                                const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
-                                int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
-                                void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream, int tile_n);
+#define PLQ_GEMM_AUTO          0
+#define PLQ_GEMM_128x128       1   /* one CTA per 128 x 128 tile, two accumulator stages */
+#define PLQ_GEMM_128x256       2   /* one CTA per 128 x 256 tile */
+#define PLQ_GEMM_PAIR_256x256  3   /* a CTA pair per 256 x 256 tile (tcgen05.mma.cta_group::2) */
+PLQ_API int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+                                   const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+                                   int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
+                                   void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream, int variant);
 
 /*
  * Decode GEMV, m <= 8: same contract as plq_mixed_gemm but streaming the weights once from

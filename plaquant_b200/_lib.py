@@ -20,7 +20,7 @@ SIGNATURES = {
     "plq_rmsnorm_pack": (_i32, [_vp, _vp, _f32, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _vp]),
     "plq_unpack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "plq_mixed_gemm": (_i32, [_vp] * 8 + [_i64] * 4 + [_vp, _i64, _vp, _vp]),
-    "plq_mixed_gemm_tile": (_i32, [_vp] * 8 + [_i64] * 4 + [_vp, _i64, _vp, _vp, _i32]),
+    "plq_mixed_gemm_variant": (_i32, [_vp] * 8 + [_i64] * 4 + [_vp, _i64, _vp, _vp, _i32]),
     "plq_gemv": (_i32, [_vp] * 8 + [_i64] * 4 + [_vp, _i64, _vp]),
 }
 

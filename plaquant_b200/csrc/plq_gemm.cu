@@ -1,20 +1,31 @@
 // Fused mixed NVFP4 / MXFP8 GEMM for sm_100a:  Y[m, n] = deq(A)[m, :] . deq(B)[n, :]  (bf16 out)
 //
-// One persistent, warp-specialised kernel.  Per 128 x BN output tile a single float32
-// accumulator lives in tensor memory; the NVFP4 K-range is issued as tcgen05.mma
-// kind::mxf4nvf4 (K = 64 per instruction, four E4M3 scales per row) and the MXFP8 K-range as
-// kind::mxf8f6f4 (K = 32 per instruction, one E8M0 scale per row) on top of the same columns.
+// One persistent, warp-specialised kernel.  Per output tile a single float32 accumulator lives
+// in tensor memory; the NVFP4 K-range is issued as tcgen05.mma kind::mxf4nvf4 (K = 64 per
+// instruction, four E4M3 scales per row) and the MXFP8 K-range as kind::mxf8f6f4 (K = 32 per
+// instruction, one E8M0 scale per row) on top of the same columns.
 //
-//   warp 0   producer: TMA loads of A/B code tiles (128-byte swizzled rows, K-major) and bulk
-//            copies of the pre-tiled scale chunks into a ring of shared-memory stages
-//   warp 1   MMA issuer: copies the scale chunks shared -> tensor memory (tcgen05.cp), issues
-//            the MMAs, releases stages and publishes finished accumulators via tcgen05.commit
-//   warps 4+ epilogue: tcgen05.ld the accumulator to registers, release it, convert to bf16, store
+// Two shapes of the same kernel (template parameter CG):
+//   CG = 1  one CTA computes a 128 x BN tile.
+//   CG = 2  a CTA pair (thread-block cluster of two, one TPC) computes a 256 x 256 tile with
+//           tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and one half (128
+//           rows) of B, so the bytes a CTA pulls from L2 per MMA drop by 30 % - the fetch rate
+//           from L2, not the tensor pipe, is what bounds this kernel.
+//
+//   warp 0     producer: TMA loads of the A/B code tiles (128-byte swizzled rows, K-major) and bulk
+//              copies of the pre-tiled scale chunks into a ring of shared-memory stages
+//   warp 1     MMA issuer (in the leader CTA of a pair): issues the MMAs, releases stages and
+//              publishes finished accumulators via tcgen05.commit.  In the second CTA of a pair
+//              this warp relays "my stage has landed" to the leader.
+//   warps 4-7  scale loaders: move each stage's scale chunks shared memory -> registers ->
+//              tensor memory (tcgen05.st), one warp per lane quadrant, into one of four rotating
+//              sets of scale columns.  Done by ordinary warps because a tcgen05.cp on the MMA
+//              thread executes in order with the MMAs and cost a third of the tensor pipe's time.
+//   warps 8+   epilogue: tcgen05.ld the accumulator to registers, release it, convert to bf16, store
 //
 // A stage holds 128 bytes of K per row for both phases: 256 NVFP4 elements (four MMAs) or
 // 128 MXFP8 elements (four MMAs).  Scale chunks are 512 bytes = 128 rows x 4 scales in the order
-// tensor memory wants (row r -> lane r % 32, column r / 32, byte = scale index), so one
-// tcgen05.cp.32x128b.warpx4 per chunk places them.
+// tensor memory wants (row r -> lane r % 32, column r / 32, byte = scale index).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records PLQ_DEV_TIMEOUT in the caller's
 // status word, all roles leave their loops, outstanding copies get time to land, tensor memory
@@ -30,26 +41,31 @@ constexpr int kBM = 128;
 constexpr int kStageKBytes = 128;                 // bytes of K per row per stage (one swizzle span)
 constexpr int kABytes = kBM * kStageKBytes;       // 16 KiB
 constexpr int kSfChunk = 512;
-constexpr int kFirstEpiWarp = 4;
+constexpr int kLoaderWarp0 = 4;                   // warps 4..7: one per tensor-memory lane quadrant
+constexpr int kFirstEpiWarp = 8;
+constexpr int kSfSets = 4;
 
-template <int BN>
+template <int BN, int CG, bool SFCP>
 struct GemmCfg {
-  static_assert(BN == 128 || BN == 256, "tile N");
+  static_assert((BN == 128 && CG == 1) || BN == 256, "tile shapes: 128x128, 128x256, pair 256x256");
   static constexpr int kAccStages = BN == 128 ? 2 : 1;
   static constexpr int kEpiColSplit = BN == 128 ? 1 : 2;     // column groups handled by different warps
   static constexpr int kEpiWarps = 4 * kEpiColSplit;
   static constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
-  static constexpr int kBBytes = BN * kStageKBytes;
-  static constexpr int kSfaBytes = 4 * kSfChunk;             // four K chunks of 128 rows
-  static constexpr int kSfbBytes = 4 * kSfChunk * (BN / 128);
+  static constexpr int kBRows = BN / CG;                     // B rows staged by one CTA
+  static constexpr int kBBytes = kBRows * kStageKBytes;
+  static constexpr int kSfGroups = BN / 128;                 // 128-row groups of B scales (all of them, in each CTA)
+  static constexpr int kSfaBytes = 4 * kSfChunk;
+  static constexpr int kSfbBytes = 4 * kSfChunk * kSfGroups;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kStages = (BN == 128) ? 6 : (CG == 2 ? 5 : 4);
   static constexpr int kTmemCols = 512;
-  static constexpr int kSfaCol = kAccStages * BN;            // 16 columns (4 MMAs x 4)
-  static constexpr int kSfbCol = kSfaCol + 16;               // 4 MMAs x BN/32
+  static constexpr int kSfSetCols = 16 + 4 * (BN / 32);      // 4 MMAs x (4 A columns + BN/32 B columns)
+  static constexpr int kSfCol0 = kAccStages * BN;
   static constexpr int kColsPerEpiWarp = BN / kEpiColSplit;  // 128
-  static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256;
-  static_assert(kSfbCol + 4 * (BN / 32) <= kTmemCols, "tensor memory budget");
+  static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 512;
+  static_assert(kSfCol0 + kSfSets * kSfSetCols <= kTmemCols, "tensor memory budget");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 struct GemmArgs {
@@ -61,10 +77,10 @@ struct GemmArgs {
   int64_t ldy;
   int32_t* status;
   int m, n, k_lo, k_hi;
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n;            // tiles_m counts 128 * CG row tiles
   int lo_stages, hi_stages;        // K stages per tile in each phase
   int lo_chunks, hi_chunks;        // scale chunks per 128-row group
-  int n_sf_groups;                 // 128-row groups present in the B scale buffers
+  int m_sf_groups, n_sf_groups;    // 128-row groups present in the A / B scale buffers
 };
 
 // Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
@@ -86,60 +102,76 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
   d |= static_cast<uint64_t>(1) << 46;
   return d;
 }
-// Instruction descriptor of a block-scaled MMA (M = 128, K-major operands).
+// Instruction descriptor of a block-scaled MMA (K-major operands).
 //   [4,6) B scale id  [7,10) A format  [10,13) B format  [17,23) N/8  [23] scale format
 //   [24,29) M/16  [29,31) A scale id
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t n, uint32_t scale_is_e8m0) {
-  return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (scale_is_e8m0 << 23) | ((128u >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t scale_is_e8m0) {
+  return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (scale_is_e8m0 << 23) | ((m >> 4) << 24);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
+template <int BN, int CG, bool SFCP>
+__global__ void __launch_bounds__(GemmCfg<BN, CG, SFCP>::kThreads, 1)
 mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_constant__ CUtensorMap tm_b_lo,
                   const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_b_hi,
                   const GemmArgs g) {
-  using C = GemmCfg<BN>;
+  using C = GemmCfg<BN, CG, SFCP>;
   extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment for the swizzled tiles
+  // 1024-byte alignment for the swizzled tiles (identical in both CTAs of a pair)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tail = smem + static_cast<size_t>(C::kStages) * C::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
-  uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* acc_full = empty_bar + C::kStages;
-  uint64_t* acc_empty = acc_full + C::kAccStages;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);      // stage landed in this CTA        (1 + tx)
+  uint64_t* peer_full = full_bar + C::kStages;                 // leader: stage landed in the peer (1, remote)
+  uint64_t* empty_bar = peer_full + C::kStages;                // stage free                       (1 commit + 4 loaders)
+  uint64_t* sf_ready = empty_bar + C::kStages;                 // leader: scale set written        (4 * CG)
+  uint64_t* sf_free = sf_ready + kSfSets;                      // scale set consumed               (1 commit)
+  uint64_t* acc_full = sf_free + kSfSets;                      // accumulator complete             (1 commit)
+  uint64_t* acc_empty = acc_full + C::kAccStages;              // leader: accumulator drained      (epi warps * CG)
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_index();
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;      // 0 = leader
+  const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&peer_full[s], 1);
+      mbar_init(&empty_bar[s], SFCP ? 1 : 1 + 4);
+    }
+    for (int s = 0; s < kSfSets; ++s) {
+      mbar_init(&sf_ready[s], 4 * CG);
+      mbar_init(&sf_free[s], 1);
     }
     for (int s = 0; s < C::kAccStages; ++s) {
       mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], C::kEpiWarps);
+      mbar_init(&acc_empty[s], C::kEpiWarps * CG);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == 0 && elect_one()) {
     if (g.k_lo) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); }
     if (g.k_hi) { prefetch_tmap(&tm_a_hi); prefetch_tmap(&tm_b_hi); }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, C::kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<CG>(tmem_holder, C::kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) {          // the peer's barriers must be initialised before anyone signals them
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   const int num_tiles = g.tiles_m * g.tiles_n;
   const int k_stages = g.lo_stages + g.hi_stages;
+  const int first_tile = CG == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+  const int tile_step = CG == 2 ? static_cast<int>(nclusters_x()) : static_cast<int>(gridDim.x);
 
   auto stage_a = [&](int s) { return smem + static_cast<size_t>(s) * C::kStageBytes; };
   auto stage_b = [&](int s) { return stage_a(s) + kABytes; };
@@ -148,13 +180,15 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
 
   if (warp == 0) {
     // ================================ producer ================================
-    if (lane == 0) {
+    if (elect_one()) {
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
-        const int m0 = tm * kBM, n0 = tn * BN;
+        const int mgrp = tm * CG + static_cast<int>(rank);        // this CTA's 128-row group of A
+        const int m0 = mgrp * kBM;
+        const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;
         for (int ks = 0; ks < k_stages; ++ks) {
           ok = mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag);
           if (!ok) break;
@@ -164,17 +198,19 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
           const int chunk0 = lo ? kk * 4 : kk;
           const int nchunk = lo ? min(4, g.lo_chunks - chunk0) : 1;
           const int chunks_k = lo ? g.lo_chunks : g.hi_chunks;
-          const uint8_t* sfa = (lo ? g.a_lo_sf : g.a_hi_sf) + (static_cast<size_t>(tm) * chunks_k + chunk0) * kSfChunk;
+          const uint8_t* sfa_base = lo ? g.a_lo_sf : g.a_hi_sf;
           const uint8_t* sfb_base = lo ? g.b_lo_sf : g.b_hi_sf;
-          int groups = 0;
-          for (int h = 0; h < BN / 128; ++h) groups += (tn * (BN / 128) + h) < g.n_sf_groups;
-          const uint32_t bytes = kABytes + C::kBBytes + static_cast<uint32_t>(nchunk) * kSfChunk * (1 + groups);
+          int groups = mgrp < g.m_sf_groups ? 1 : 0;
+          for (int h = 0; h < C::kSfGroups; ++h) groups += (tn * C::kSfGroups + h) < g.n_sf_groups;
+          const uint32_t bytes = kABytes + C::kBBytes + static_cast<uint32_t>(nchunk) * kSfChunk * groups;
           mbar_arrive_expect_tx(&full_bar[s], bytes);
           tma_load_2d(stage_a(s), lo ? &tm_a_lo : &tm_a_hi, kk * kStageKBytes, m0, &full_bar[s]);
           tma_load_2d(stage_b(s), lo ? &tm_b_lo : &tm_b_hi, kk * kStageKBytes, n0, &full_bar[s]);
-          bulk_g2s(stage_sfa(s), sfa, nchunk * kSfChunk, &full_bar[s]);
-          for (int h = 0; h < BN / 128; ++h) {
-            const int grp = tn * (BN / 128) + h;
+          if (mgrp < g.m_sf_groups)
+            bulk_g2s(stage_sfa(s), sfa_base + (static_cast<size_t>(mgrp) * chunks_k + chunk0) * kSfChunk,
+                     nchunk * kSfChunk, &full_bar[s]);
+          for (int h = 0; h < C::kSfGroups; ++h) {
+            const int grp = tn * C::kSfGroups + h;
             if (grp < g.n_sf_groups)
               bulk_g2s(stage_sfb(s) + h * 4 * kSfChunk,
                        sfb_base + (static_cast<size_t>(grp) * chunks_k + chunk0) * kSfChunk, nchunk * kSfChunk,
@@ -185,64 +221,138 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    // ================================ MMA issuer ================================
-    if (lane == 0) {
-      constexpr uint32_t idesc_lo = make_idesc(1u /*E2M1*/, BN, 0u /*UE4M3*/);
-      constexpr uint32_t idesc_hi = make_idesc(0u /*E4M3*/, BN, 1u /*UE8M0*/);
-      const uint32_t sfa_t = tmem_base + C::kSfaCol;
-      const uint32_t sfb_t = tmem_base + C::kSfbCol;
-      int s = 0, as = 0;
-      uint32_t phase = 0, aphase = 0;
+    const bool elected = elect_one();
+    if (elected && leader) {
+      // ================================ MMA issuer ================================
+      constexpr uint32_t idesc_lo = make_idesc(1u /*E2M1*/, 128u * CG, BN, 0u /*UE4M3*/);
+      constexpr uint32_t idesc_hi = make_idesc(0u /*E4M3*/, 128u * CG, BN, 1u /*UE8M0*/);
+      // barrier addresses to commit to: own CTA and, for a pair, the same barrier in the peer
+      const uint32_t peer_off = CG == 2 ? map_to_cta(smem_u32(full_bar), 1u) - smem_u32(full_bar) : 0u;
+      auto commit_all = [&](uint64_t* bar) {
+        tc_commit<CG>(smem_u32(bar));
+        if constexpr (CG == 2) tc_commit<CG>(smem_u32(bar) + peer_off);
+      };
+      int s = 0, as = 0, set = 0;
+      uint32_t phase = 0, aphase = 0, sphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        ok = mbar_wait_bounded(&acc_empty[as], aphase ^ 1, abort_flag);
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        ok = CG == 2 ? mbar_wait_bounded_cluster(&acc_empty[as], aphase ^ 1, abort_flag)
+                     : mbar_wait_bounded(&acc_empty[as], aphase ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         uint32_t accumulate = 0;
         for (int ks = 0; ks < k_stages; ++ks) {
           ok = mbar_wait_bounded(&full_bar[s], phase, abort_flag);
+          if (ok && CG == 2) ok = mbar_wait_bounded_cluster(&peer_full[s], phase, abort_flag);
+          if constexpr (!SFCP) {
+            if (ok) ok = CG == 2 ? mbar_wait_bounded_cluster(&sf_ready[set], sphase, abort_flag)
+                                 : mbar_wait_bounded(&sf_ready[set], sphase, abort_flag);
+          }
           if (!ok) break;
           tc_fence_after();
           const bool lo = ks < g.lo_stages;
           const int kk = lo ? ks : ks - g.lo_stages;
-          const uint32_t a_addr = smem_u32(stage_a(s)), b_addr = smem_u32(stage_b(s));
-          const uint32_t sfa_addr = smem_u32(stage_sfa(s)), sfb_addr = smem_u32(stage_sfb(s));
-          const uint64_t adesc = make_sw128_desc(a_addr), bdesc = make_sw128_desc(b_addr);
+          const uint32_t sfa_t = tmem_base + C::kSfCol0 + set * C::kSfSetCols, sfb_t = sfa_t + 16;
+          const uint64_t adesc = make_sw128_desc(smem_u32(stage_a(s))), bdesc = make_sw128_desc(smem_u32(stage_b(s)));
+          if constexpr (SFCP) {
+            // scale chunks shared -> tensor memory on this thread, ahead of the MMAs that read them
+            const uint32_t sfa_addr = smem_u32(stage_sfa(s)), sfb_addr = smem_u32(stage_sfb(s));
+            const int nchunk = lo ? min(4, g.lo_chunks - kk * 4) : 1;
+            for (int h = 0; h < nchunk; ++h) {
+              tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, make_sf_desc(sfa_addr + h * kSfChunk));
+#pragma unroll
+              for (int q = 0; q < C::kSfGroups; ++q)
+                tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, make_sf_desc(sfb_addr + (q * 4 + h) * kSfChunk));
+            }
+          }
           if (lo) {
             const int nmma = min(4, g.lo_chunks - kk * 4);
             for (int h = 0; h < nmma; ++h) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * h, make_sf_desc(sfa_addr + h * kSfChunk));
-#pragma unroll
-              for (int q = 0; q < BN / 128; ++q)
-                tc_cp_32x128b_warpx4(sfb_t + (BN / 32) * h + 4 * q, make_sf_desc(sfb_addr + (q * 4 + h) * kSfChunk));
-            }
-            for (int h = 0; h < nmma; ++h) {
               // advance 32 bytes (64 E2M1) inside the swizzle span: +2 in the address field
-              tc_mma_nvf4(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc_lo, sfa_t + 4 * h, sfb_t + (BN / 32) * h,
-                          accumulate);
+              tc_mma_nvf4<CG>(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc_lo, sfa_t + 4 * h, sfb_t + (BN / 32) * h,
+                              accumulate);
               accumulate = 1;
             }
           } else {
             const int nmma = min(4, (g.k_hi - kk * 128) / 32);
-            tc_cp_32x128b_warpx4(sfa_t, make_sf_desc(sfa_addr));
-#pragma unroll
-            for (int q = 0; q < BN / 128; ++q)
-              tc_cp_32x128b_warpx4(sfb_t + 4 * q, make_sf_desc(sfb_addr + q * 4 * kSfChunk));
             for (int h = 0; h < nmma; ++h) {
               // scale id h selects byte h of every scale column; mirrored in the address' top bits
               const uint32_t idesc = idesc_hi | (static_cast<uint32_t>(h) << 4) | (static_cast<uint32_t>(h) << 29);
-              tc_mma_mxf8(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc, sfa_t + (static_cast<uint32_t>(h) << 30),
-                          sfb_t + (static_cast<uint32_t>(h) << 30), accumulate);
+              tc_mma_mxf8<CG>(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc, sfa_t + (static_cast<uint32_t>(h) << 30),
+                              sfb_t + (static_cast<uint32_t>(h) << 30), accumulate);
               accumulate = 1;
             }
           }
-          tc_commit(&empty_bar[s]);                 // stage reusable once these MMAs have read it
+          commit_all(&empty_bar[s]);                 // stage reusable once these MMAs have read it
+          if constexpr (!SFCP) commit_all(&sf_free[set]);   // and so is the set of scale columns
           if (++s == C::kStages) { s = 0; phase ^= 1; }
+          if (++set == kSfSets) { set = 0; sphase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&acc_full[as]);                   // accumulator complete
+        commit_all(&acc_full[as]);                   // accumulator complete (in both CTAs of a pair)
         if (++as == C::kAccStages) { as = 0; aphase ^= 1; }
+      }
+    } else if (elected && CG == 2) {
+      // ============ second CTA of a pair: tell the leader when a stage has landed here ============
+      const uint32_t remote = map_to_cta(smem_u32(peer_full), 0u);
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        for (int ks = 0; ks < k_stages; ++ks) {
+          ok = mbar_wait_bounded(&full_bar[s], phase, abort_flag);
+          if (!ok) break;
+          mbar_arrive_cluster(remote + 8u * s);
+          if (++s == C::kStages) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (!SFCP && warp >= kLoaderWarp0 && warp < kLoaderWarp0 + 4) {
+    // ================================ scale loaders ================================
+    // Warp q fills lanes [32q, 32q+32) of the scale columns: lane i holds rows i, i+32, i+64, i+96 of
+    // a 128-row group, i.e. the 16 bytes at offset 16*i of a chunk are its four columns.
+    const int quad = warp & 3;
+    const uint32_t ready_addr = CG == 2 ? map_to_cta(smem_u32(sf_ready), 0u) : smem_u32(sf_ready);
+    int s = 0, set = 0;
+    uint32_t phase = 0, sphase = 0;
+    bool ok = true;
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int ks = 0; ks < k_stages; ++ks) {
+        ok = mbar_wait_bounded_warp(&full_bar[s], phase, abort_flag);
+        if (ok) ok = mbar_wait_bounded_warp(&sf_free[set], sphase ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t col = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + C::kSfCol0 + set * C::kSfSetCols;
+        const uint4* sfa = reinterpret_cast<const uint4*>(stage_sfa(s)) + lane;
+        const uint4* sfb = reinterpret_cast<const uint4*>(stage_sfb(s)) + lane;
+        uint32_t r[16];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {               // A scales: columns 4h .. 4h+3
+          const uint4 v = sfa[h * 32];
+          r[4 * h] = v.x; r[4 * h + 1] = v.y; r[4 * h + 2] = v.z; r[4 * h + 3] = v.w;
+        }
+        tc_st_32x32b_x16(col, r);
+#pragma unroll
+        for (int half = 0; half < C::kSfGroups; ++half) {   // B scales: columns 16 + (BN/32) h + 4 q
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int idx = half * 4 + i;           // position in column order: h = idx / groups, q = idx % groups
+            const int h = idx / C::kSfGroups, q = idx % C::kSfGroups;
+            const uint4 v = sfb[(q * 4 + h) * 32];
+            r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+          }
+          tc_st_32x32b_x16(col + 16 + half * 16, r);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_cluster(ready_addr + 8u * set);   // scales of this stage are in tensor memory
+          mbar_arrive(&empty_bar[s]);                   // and no longer needed in shared memory
+        }
+        if (++s == C::kStages) { s = 0; phase ^= 1; }
+        if (++set == kSfSets) { set = 0; sphase ^= 1; }
       }
     }
   } else if (warp >= kFirstEpiWarp) {
@@ -250,15 +360,15 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
     const int e = warp - kFirstEpiWarp;
     const int quad = warp & 3;                      // tensor-memory lane quadrant this warp may read
     const int cgp = e >> 2;                         // column group
+    const uint32_t empty_addr = CG == 2 ? map_to_cta(smem_u32(acc_empty), 0u) : smem_u32(acc_empty);
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
-      const int row = tm * kBM + quad * 32 + lane;
+      const int row = (tm * CG + static_cast<int>(rank)) * kBM + quad * 32 + lane;
       const int col0 = tn * BN + cgp * C::kColsPerEpiWarp;
-      ok = mbar_wait_bounded(&acc_full[as], aphase, abort_flag);
-      ok = __all_sync(0xFFFFFFFFu, ok);
+      ok = mbar_wait_bounded_warp(&acc_full[as], aphase, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN + cgp * C::kColsPerEpiWarp;
@@ -277,7 +387,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[as]);   // accumulator drained: the next tile may start
+      if (lane == 0) mbar_arrive_cluster(empty_addr + 8u * as);   // drained: the next tile may start
       if (++as == C::kAccStages) { as = 0; aphase ^= 1; }
       if (row < g.m) {
         __nv_bfloat16* yrow = g.y + static_cast<size_t>(row) * g.ldy;
@@ -301,9 +411,14 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (CG == 2) {          // the leader's MMAs read the peer's shared memory: leave together
+    tc_fence_before();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    tmem_dealloc<CG>(tmem_base, C::kTmemCols);
   }
 }
 
@@ -338,46 +453,59 @@ static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t ro
   return r == CUDA_SUCCESS ? PLQ_OK : PLQ_ERR_TENSORMAP;
 }
 
-template <int BN>
+template <int BN, int CG, bool SFCP>
 static int launch_gemm(const void* a_lo, const void* a_hi, const void* b_lo, const void* b_hi, GemmArgs& g,
                        cudaStream_t stream) {
-  using C = GemmCfg<BN>;
+  using C = GemmCfg<BN, CG, SFCP>;
   CUtensorMap tm_a_lo, tm_b_lo, tm_a_hi, tm_b_hi;
   memset(&tm_a_lo, 0, sizeof(CUtensorMap)); memset(&tm_b_lo, 0, sizeof(CUtensorMap));
   memset(&tm_a_hi, 0, sizeof(CUtensorMap)); memset(&tm_b_hi, 0, sizeof(CUtensorMap));
   int st;
   if (g.k_lo) {
     if ((st = make_tmap(&tm_a_lo, a_lo, g.m, g.k_lo / 2, kBM)) != PLQ_OK) return st;
-    if ((st = make_tmap(&tm_b_lo, b_lo, g.n, g.k_lo / 2, BN)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm_b_lo, b_lo, g.n, g.k_lo / 2, C::kBRows)) != PLQ_OK) return st;
   }
   if (g.k_hi) {
     if ((st = make_tmap(&tm_a_hi, a_hi, g.m, g.k_hi, kBM)) != PLQ_OK) return st;
-    if ((st = make_tmap(&tm_b_hi, b_hi, g.n, g.k_hi, BN)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm_b_hi, b_hi, g.n, g.k_hi, C::kBRows)) != PLQ_OK) return st;
   }
-  g.tiles_m = (g.m + kBM - 1) / kBM;
+  g.tiles_m = (g.m + kBM * CG - 1) / (kBM * CG);
   g.tiles_n = (g.n + BN - 1) / BN;
+  auto kernel = mixed_gemm_kernel<BN, CG, SFCP>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   PLQ_CUDA_TRY(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    PLQ_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    PLQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(C::kSmemBytes)));
     attr_dev = dev;
   }
   const int tiles = g.tiles_m * g.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  mixed_gemm_kernel<BN><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tm_a_lo, tm_b_lo, tm_a_hi, tm_b_hi, g);
-  PLQ_CUDA_TRY(cudaGetLastError());
+  const int slots = sm_count() / CG;                 // CTAs (CG = 1) or CTA pairs (CG = 2) resident at once
+  const int groups = tiles < slots ? tiles : slots;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(groups * CG), 1, 1);
+  cfg.blockDim = dim3(C::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm_a_lo, tm_b_lo, tm_a_hi, tm_b_hi, g));
   return PLQ_OK;
 }
 
 }  // namespace plq
 
-extern "C" int plq_mixed_gemm_tile(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes,
+extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes,
                                    const void* a_hi_sf, const void* b_lo_codes, const void* b_lo_sf,
                                    const void* b_hi_codes, const void* b_hi_sf, int64_t m, int64_t n, int64_t k_lo,
                                    int64_t k_hi, void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream,
-                                   int tile_n) {
+                                   int variant) {
   using namespace plq;
   if (m < 1 || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0) return PLQ_ERR_SHAPE;
   if (k_lo % 64 != 0 || k_hi % 32 != 0 || n % 8 != 0 || ldy % 8 != 0 || ldy < n) return PLQ_ERR_SHAPE;
@@ -403,10 +531,24 @@ extern "C" int plq_mixed_gemm_tile(const void* a_lo_codes, const void* a_lo_sf, 
   g.hi_chunks = static_cast<int>((k_hi + 127) / 128);
   g.lo_stages = (g.lo_chunks + 3) / 4;
   g.hi_stages = g.hi_chunks;
+  g.m_sf_groups = static_cast<int>((m + 127) / 128);
   g.n_sf_groups = static_cast<int>((n + 127) / 128);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (tile_n == 128) return launch_gemm<128>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
-  if (tile_n == 256) return launch_gemm<256>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == PLQ_GEMM_AUTO) {
+    // A CTA pair needs 30 % fewer bytes from L2 per MMA, which is what bounds large problems;
+    // small ones are better off with more, smaller tiles.
+    const int sms = sm_count();
+    const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    const int64_t wide_tiles = ((m + 127) / 128) * ((n + 255) / 256);
+    if (n >= 256 && pair_tiles >= sms / 2) variant = PLQ_GEMM_PAIR_256x256;
+    else if (n >= 256 && (wide_tiles >= sms || n % 256 == 0)) variant = PLQ_GEMM_128x256;
+    else variant = PLQ_GEMM_128x128;
+  }
+  if (variant == PLQ_GEMM_128x128) return launch_gemm<128, 1, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == PLQ_GEMM_128x256) return launch_gemm<256, 1, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == PLQ_GEMM_PAIR_256x256) return launch_gemm<256, 2, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == 12) return launch_gemm<256, 1, false>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == 13) return launch_gemm<256, 2, false>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
   return PLQ_ERR_SHAPE;
 }
 
@@ -414,9 +556,6 @@ extern "C" int plq_mixed_gemm(const void* a_lo_codes, const void* a_lo_sf, const
                               const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
                               int64_t m, int64_t n, int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy,
                               int32_t* dev_status, void* stream) {
-  // Wide tiles halve the shared-memory traffic per MMA; narrow ones give small problems more CTAs.
-  const int64_t tiles256 = ((m + 127) / 128) * ((n + 255) / 256);
-  const int tile_n = (tiles256 >= plq::sm_count() || n % 256 == 0) && n >= 256 ? 256 : 128;
-  return plq_mixed_gemm_tile(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf, m,
-                             n, k_lo, k_hi, y_bf16, ldy, dev_status, stream, tile_n);
+  return plq_mixed_gemm_variant(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf,
+                                m, n, k_lo, k_hi, y_bf16, ldy, dev_status, stream, PLQ_GEMM_AUTO);
 }

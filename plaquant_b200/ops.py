@@ -133,9 +133,13 @@ def _check_pair(a: PackedMatrix, b: PackedMatrix, layout: int) -> None:
         raise ValueError("scale buffers are in the wrong layout for this kernel")
 
 
+GEMM_VARIANTS = {None: 0, "auto": 0, "128x128": 1, "128x256": 2, "pair256x256": 3, "128x256-st": 12, "pair256x256-st": 13}
+
+
 def mixed_gemm(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
-               tile_n: Optional[int] = None) -> torch.Tensor:
-    """y[m, n] = deq(a) @ deq(b).T, bf16, via the fused tcgen05 kernel (tiled scale layout)."""
+               variant: Optional[str] = None) -> torch.Tensor:
+    """y[m, n] = deq(a) @ deq(b).T, bf16, via the fused tcgen05 kernel (tiled scale layout).
+    `variant` picks the tile shape ("128x128", "128x256", "pair256x256"); default: heuristic."""
     _check_pair(a, b, SF_TILED)
     y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
     L = _lib.lib()
@@ -143,7 +147,7 @@ def mixed_gemm(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = N
             _ptr(b.lo_codes), _ptr(b.lo_sf), _ptr(b.hi_codes), _ptr(b.hi_sf),
             a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0), _ptr(status_word(a.device)), _stream(a.device)]
     with torch.cuda.device(a.device):
-        st = L.plq_mixed_gemm(*args) if tile_n is None else L.plq_mixed_gemm_tile(*args, int(tile_n))
+        st = L.plq_mixed_gemm_variant(*args, GEMM_VARIANTS[variant])
     _lib.check(st)
     return y
 

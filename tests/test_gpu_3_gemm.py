@@ -15,6 +15,7 @@ pytestmark = pytest.mark.gpu
 plq = pytest.importorskip("plaquant_b200")
 
 TOL = 1e-3
+VARIANTS = ["128x128", "128x256", "pair256x256"]
 
 
 def _to_device(pd: dict, layout: str):
@@ -34,14 +35,14 @@ def _oracle_bf16(pa: dict, pb: dict) -> np.ndarray:
     return F.round_to_bf16(F.linear(pa, pb))
 
 
-def _run(pa_dev, pb_dev, tile_n):
-    y = plq.mixed_gemm(pa_dev, pb_dev, tile_n=tile_n)
+def _run(pa_dev, pb_dev, variant):
+    y = plq.mixed_gemm(pa_dev, pb_dev, variant=variant)
     plq.check_device_status()
     return f32_of(y)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
-def test_known_answer_all_ones(tile_n):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_known_answer_all_ones(variant):
     """Codes 1.0, scales 1.0: every output equals K.  Catches descriptor / pipeline errors."""
     m, n, k_lo, k_hi = 128, 256, 512, 128
     pa = {"rows": m, "k_lo": k_lo, "k_hi": k_hi, "lo_codes": np.full((m, k_lo // 2), 0x22, np.uint8),
@@ -50,12 +51,12 @@ def test_known_answer_all_ones(tile_n):
     pb = {**pa, "rows": n, "lo_codes": np.full((n, k_lo // 2), 0x22, np.uint8),
           "lo_sf": np.full((n, k_lo // 16), 0x38, np.uint8), "hi_codes": np.full((n, k_hi), 0x38, np.uint8),
           "hi_sf": np.full((n, k_hi // 32), 127, np.uint8)}
-    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), tile_n)
+    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), variant)
     assert np.array_equal(y, np.full((m, n), float(k_lo + k_hi), np.float32))
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
-def test_known_answer_layout_probes(tile_n):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_known_answer_layout_probes(variant):
     """Row-, column-, K- and scale-dependent patterns with exactly representable results, so any
     permutation of rows, columns, K blocks, nibbles or scale bytes shows up as a wrong integer."""
     rng = np.random.default_rng(5)
@@ -69,7 +70,7 @@ def test_known_answer_layout_probes(tile_n):
                 "hi_codes": hi, "hi_sf": rng.integers(124, 131, (rows, k_hi // 32), dtype=np.uint8)}
     pa, pb = mk(m), mk(n)
     want = F.linear(pa, pb)
-    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), tile_n)
+    y = _run(_to_device(pa, "tiled"), _to_device(pb, "tiled"), variant)
     assert rel_l2(y, F.round_to_bf16(want)) <= TOL
 
 
@@ -77,14 +78,14 @@ def test_known_answer_layout_probes(tile_n):
     (128, 128, 256, 0), (128, 256, 256, 128), (7, 136, 192, 64), (129, 8, 128, 64), (300, 392, 1024, 448),
     (64, 264, 128, 128), (16, 4096, 4096, 128), (130, 640, 14336, 448),
 ])
-@pytest.mark.parametrize("tile_n", [128, 256])
-def test_random_shapes_against_oracle(m, n, k, k_hi, tile_n):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_random_shapes_against_oracle(m, n, k, k_hi, variant):
     x = synth_activation(m, k, seed=m + k)
     w = synth_weight(n, k, seed=n + k + 1)
     had = k % 128 == 0
     pa = plq.pack(x.cuda(), k_hi, hadamard=had, sf_layout="tiled")
     pb = plq.pack(w.cuda(), k_hi, hadamard=had, sf_layout="tiled")
-    y = _run(pa, pb, tile_n)
+    y = _run(pa, pb, variant)
     want = _oracle_bf16(packed_to_numpy(pa), packed_to_numpy(pb))
     r = rel_l2(y, want)
     assert r <= TOL, r
