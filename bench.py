@@ -417,7 +417,7 @@ def main():
                     help="run one kernel on one fixed case instead of the full step")
     ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
     ap.add_argument("--m", type=int, default=None)
-    ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256", "128x256-st", "pair256x256-st"])
+    ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

@@ -141,6 +141,34 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, in
       : "memory");
 }
 
+// Tiled TMA loads for kernels that may run as a CTA pair.  CG = 2 uses the pair form of the
+// instruction, whose completion bytes may be counted on an mbarrier of the other CTA of the
+// pair: `bar_addr` is a shared::cluster address (clear bit 24 of a local address to name the
+// even-ranked CTA's copy of the barrier).  No multicast: each CTA loads only its own tile.
+template <int CG>
+__device__ __forceinline__ void tma_load_2d_cg(uint32_t dst, const void* tmap, int32_t x, int32_t y, uint32_t bar_addr) {
+  if constexpr (CG == 1)
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar_addr) : "memory");
+  else
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar_addr) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tma_load_3d_cg(uint32_t dst, const void* tmap, int32_t x, int32_t y, int32_t z,
+                                               uint32_t bar_addr) {
+  if constexpr (CG == 1)
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+  else
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

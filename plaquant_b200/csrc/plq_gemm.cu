@@ -9,23 +9,27 @@
 //   CG = 1  one CTA computes a 128 x BN tile.
 //   CG = 2  a CTA pair (thread-block cluster of two, one TPC) computes a 256 x 256 tile with
 //           tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and one half (128
-//           rows) of B, so the bytes a CTA pulls from L2 per MMA drop by 30 % - the fetch rate
-//           from L2, not the tensor pipe, is what bounds this kernel.
+//           rows) of B, so a CTA pulls 30 % fewer bytes from L2 per MMA.
 //
-//   warp 0     producer: TMA loads of the A/B code tiles (128-byte swizzled rows, K-major) and bulk
-//              copies of the pre-tiled scale chunks into a ring of shared-memory stages
-//   warp 1     MMA issuer (in the leader CTA of a pair): issues the MMAs, releases stages and
-//              publishes finished accumulators via tcgen05.commit.  In the second CTA of a pair
-//              this warp relays "my stage has landed" to the leader.
-//   warps 4-7  scale loaders: move each stage's scale chunks shared memory -> registers ->
-//              tensor memory (tcgen05.st), one warp per lane quadrant, into one of four rotating
-//              sets of scale columns.  Done by ordinary warps because a tcgen05.cp on the MMA
-//              thread executes in order with the MMAs and cost a third of the tensor pipe's time.
-//   warps 8+   epilogue: tcgen05.ld the accumulator to registers, release it, convert to bf16, store
+//   warps 0, 2  producers, taking alternate K stages: TMA loads of the A/B code tiles (128-byte
+//               swizzled rows, K-major) and bulk copies of the pre-tiled scale chunks into a ring of
+//               shared-memory stages.  Two of them because one thread's issue rate (barrier wait,
+//               expect-tx, five copy instructions: ~770 cycles measured) is longer than the 512
+//               cycles the tensor pipe needs per stage.
+//   warp 1      MMA issuer (leader CTA of a pair): copies the stage's scale chunks shared -> tensor
+//               memory (tcgen05.cp), issues the MMAs, releases the stage and publishes finished
+//               accumulators with tcgen05.commit.  In the second CTA of a pair this warp relays
+//               "my stage has landed" to the leader.
+//   warps 4+    epilogue: tcgen05.ld the accumulator to registers, release it, convert to bf16, store
+//
+// The single threads that issue TMA / tcgen05 instructions are chosen with elect.sync inside a
+// warp-uniform branch: the compiler then keeps descriptors in uniform registers; with a plain
+// `lane == 0` test the same instruction stream issued about three times slower (measured).
 //
 // A stage holds 128 bytes of K per row for both phases: 256 NVFP4 elements (four MMAs) or
 // 128 MXFP8 elements (four MMAs).  Scale chunks are 512 bytes = 128 rows x 4 scales in the order
-// tensor memory wants (row r -> lane r % 32, column r / 32, byte = scale index).
+// tensor memory wants (row r -> lane r % 32, column r / 32, byte = scale index), so one
+// tcgen05.cp.32x128b.warpx4 per chunk places them.
 //
 // Every mbarrier wait is bounded; on expiry the CTA records PLQ_DEV_TIMEOUT in the caller's
 // status word, all roles leave their loops, outstanding copies get time to land, tensor memory
@@ -41,11 +45,10 @@ constexpr int kBM = 128;
 constexpr int kStageKBytes = 128;                 // bytes of K per row per stage (one swizzle span)
 constexpr int kABytes = kBM * kStageKBytes;       // 16 KiB
 constexpr int kSfChunk = 512;
-constexpr int kLoaderWarp0 = 4;                   // warps 4..7: one per tensor-memory lane quadrant
-constexpr int kFirstEpiWarp = 8;
-constexpr int kSfSets = 4;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kProducers = 2;
 
-template <int BN, int CG, bool SFCP>
+template <int BN, int CG>
 struct GemmCfg {
   static_assert((BN == 128 && CG == 1) || BN == 256, "tile shapes: 128x128, 128x256, pair 256x256");
   static constexpr int kAccStages = BN == 128 ? 2 : 1;
@@ -61,6 +64,7 @@ struct GemmCfg {
   static constexpr int kStages = (BN == 128) ? 6 : (CG == 2 ? 5 : 4);
   static constexpr int kTmemCols = 512;
   static constexpr int kSfSetCols = 16 + 4 * (BN / 32);      // 4 MMAs x (4 A columns + BN/32 B columns)
+  static constexpr int kSfSets = 2;                          // alternate per stage
   static constexpr int kSfCol0 = kAccStages * BN;
   static constexpr int kColsPerEpiWarp = BN / kEpiColSplit;  // 128
   static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 512;
@@ -68,11 +72,13 @@ struct GemmCfg {
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
+// Tensor maps: code matrices as 2-D u8 [rows, row bytes] with 128-byte swizzled boxes; tiled
+// scale buffers as 3-D int32 [128 words = one 512-byte chunk, chunks per group, 128-row groups].
+struct GemmMaps {
+  CUtensorMap a_lo, b_lo, a_hi, b_hi, sfa_lo, sfb_lo, sfa_hi, sfb_hi;
+};
+
 struct GemmArgs {
-  const uint8_t* a_lo_sf;   // tiled
-  const uint8_t* a_hi_sf;
-  const uint8_t* b_lo_sf;
-  const uint8_t* b_hi_sf;
   __nv_bfloat16* y;
   int64_t ldy;
   int32_t* status;
@@ -80,7 +86,6 @@ struct GemmArgs {
   int tiles_m, tiles_n;            // tiles_m counts 128 * CG row tiles
   int lo_stages, hi_stages;        // K stages per tile in each phase
   int lo_chunks, hi_chunks;        // scale chunks per 128-row group
-  int m_sf_groups, n_sf_groups;    // 128-row groups present in the A / B scale buffers
 };
 
 // Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
@@ -109,22 +114,19 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint
   return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (scale_is_e8m0 << 23) | ((m >> 4) << 24);
 }
 
-template <int BN, int CG, bool SFCP>
-__global__ void __launch_bounds__(GemmCfg<BN, CG, SFCP>::kThreads, 1)
-mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_constant__ CUtensorMap tm_b_lo,
-                  const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_b_hi,
-                  const GemmArgs g) {
-  using C = GemmCfg<BN, CG, SFCP>;
+template <int BN, int CG>
+__global__ void __launch_bounds__(GemmCfg<BN, CG>::kThreads, 1)
+mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
+  using C = GemmCfg<BN, CG>;
+  const CUtensorMap& tm_a_lo = maps.a_lo;  const CUtensorMap& tm_b_lo = maps.b_lo;
+  const CUtensorMap& tm_a_hi = maps.a_hi;  const CUtensorMap& tm_b_hi = maps.b_hi;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles (identical in both CTAs of a pair)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tail = smem + static_cast<size_t>(C::kStages) * C::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);      // stage landed in this CTA        (1 + tx)
-  uint64_t* peer_full = full_bar + C::kStages;                 // leader: stage landed in the peer (1, remote)
-  uint64_t* empty_bar = peer_full + C::kStages;                // stage free                       (1 commit + 4 loaders)
-  uint64_t* sf_ready = empty_bar + C::kStages;                 // leader: scale set written        (4 * CG)
-  uint64_t* sf_free = sf_ready + kSfSets;                      // scale set consumed               (1 commit)
-  uint64_t* acc_full = sf_free + kSfSets;                      // accumulator complete             (1 commit)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);      // stage landed (leader: in both CTAs) (1 + tx)
+  uint64_t* empty_bar = full_bar + C::kStages;                // stage free                       (1 commit)
+  uint64_t* acc_full = empty_bar + C::kStages;                 // accumulator complete             (1 commit)
   uint64_t* acc_empty = acc_full + C::kAccStages;              // leader: accumulator drained      (epi warps * CG)
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -137,12 +139,7 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&peer_full[s], 1);
-      mbar_init(&empty_bar[s], SFCP ? 1 : 1 + 4);
-    }
-    for (int s = 0; s < kSfSets; ++s) {
-      mbar_init(&sf_ready[s], 4 * CG);
-      mbar_init(&sf_free[s], 1);
+      mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < C::kAccStages; ++s) {
       mbar_init(&acc_full[s], 1);
@@ -152,8 +149,8 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
     fence_barrier_init();
   }
   if (warp == 0 && elect_one()) {
-    if (g.k_lo) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); }
-    if (g.k_hi) { prefetch_tmap(&tm_a_hi); prefetch_tmap(&tm_b_hi); }
+    if (g.k_lo) { prefetch_tmap(&tm_a_lo); prefetch_tmap(&tm_b_lo); prefetch_tmap(&maps.sfa_lo); prefetch_tmap(&maps.sfb_lo); }
+    if (g.k_hi) { prefetch_tmap(&tm_a_hi); prefetch_tmap(&tm_b_hi); prefetch_tmap(&maps.sfa_hi); prefetch_tmap(&maps.sfb_hi); }
   }
   if (warp == 1) {
     tmem_alloc<CG>(tmem_holder, C::kTmemCols);
@@ -172,52 +169,46 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
   const int k_stages = g.lo_stages + g.hi_stages;
   const int first_tile = CG == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
   const int tile_step = CG == 2 ? static_cast<int>(nclusters_x()) : static_cast<int>(gridDim.x);
+  const uint32_t smem_base = smem_u32(smem);
 
-  auto stage_a = [&](int s) { return smem + static_cast<size_t>(s) * C::kStageBytes; };
-  auto stage_b = [&](int s) { return stage_a(s) + kABytes; };
-  auto stage_sfa = [&](int s) { return stage_b(s) + C::kBBytes; };
-  auto stage_sfb = [&](int s) { return stage_sfa(s) + C::kSfaBytes; };
-
-  if (warp == 0) {
-    // ================================ producer ================================
+  if (warp == 0 || warp == 2) {
+    // ================================ producers ================================
+    // Producer p takes the K stages whose running index (over all tiles of this CTA) is = p mod 2.
     if (elect_one()) {
-      int s = 0;
-      uint32_t phase = 0;
+      const int pid = warp == 0 ? 0 : 1;
+      int tile = first_tile, ks = pid;
+      while (ks >= k_stages && tile < num_tiles) { ks -= k_stages; tile += tile_step; }
+      uint32_t gs = pid;                  // running stage index: slot = gs % kStages, use count = gs / kStages
       bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      while (ok && tile < num_tiles) {
+        // ---- per tile ----
         const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
         const int mgrp = tm * CG + static_cast<int>(rank);        // this CTA's 128-row group of A
         const int m0 = mgrp * kBM;
         const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;
-        for (int ks = 0; ks < k_stages; ++ks) {
-          ok = mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag);
+        // ---- this thread's stages of the tile ----
+        for (; ks < k_stages; ks += kProducers) {
+          const uint32_t slot = gs % C::kStages;
+          ok = mbar_wait_bounded(&empty_bar[slot], ((gs / C::kStages) & 1u) ^ 1u, abort_flag);
           if (!ok) break;
           const bool lo = ks < g.lo_stages;
           const int kk = lo ? ks : ks - g.lo_stages;
-          // scale chunks of this stage: NVFP4 one per MMA (up to four), MXFP8 one per stage
-          const int chunk0 = lo ? kk * 4 : kk;
-          const int nchunk = lo ? min(4, g.lo_chunks - chunk0) : 1;
-          const int chunks_k = lo ? g.lo_chunks : g.hi_chunks;
-          const uint8_t* sfa_base = lo ? g.a_lo_sf : g.a_hi_sf;
-          const uint8_t* sfb_base = lo ? g.b_lo_sf : g.b_hi_sf;
-          int groups = mgrp < g.m_sf_groups ? 1 : 0;
-          for (int h = 0; h < C::kSfGroups; ++h) groups += (tn * C::kSfGroups + h) < g.n_sf_groups;
-          const uint32_t bytes = kABytes + C::kBBytes + static_cast<uint32_t>(nchunk) * kSfChunk * groups;
-          mbar_arrive_expect_tx(&full_bar[s], bytes);
-          tma_load_2d(stage_a(s), lo ? &tm_a_lo : &tm_a_hi, kk * kStageKBytes, m0, &full_bar[s]);
-          tma_load_2d(stage_b(s), lo ? &tm_b_lo : &tm_b_hi, kk * kStageKBytes, n0, &full_bar[s]);
-          if (mgrp < g.m_sf_groups)
-            bulk_g2s(stage_sfa(s), sfa_base + (static_cast<size_t>(mgrp) * chunks_k + chunk0) * kSfChunk,
-                     nchunk * kSfChunk, &full_bar[s]);
-          for (int h = 0; h < C::kSfGroups; ++h) {
-            const int grp = tn * C::kSfGroups + h;
-            if (grp < g.n_sf_groups)
-              bulk_g2s(stage_sfb(s) + h * 4 * kSfChunk,
-                       sfb_base + (static_cast<size_t>(grp) * chunks_k + chunk0) * kSfChunk, nchunk * kSfChunk,
-                       &full_bar[s]);
-          }
-          if (++s == C::kStages) { s = 0; phase ^= 1; }
+          const int chunk0 = lo ? kk * 4 : kk;              // NVFP4: one chunk per MMA; MXFP8: one per stage
+          const uint32_t st = smem_base + slot * C::kStageBytes;
+          // In a pair every load of both CTAs is counted on the leader's barrier, which is the one the
+          // MMA issuer waits on; boxes always have their full size (out-of-range parts are zero-filled).
+          const uint32_t bar = smem_u32(&full_bar[slot]) & (CG == 2 ? 0xFEFFFFFFu : 0xFFFFFFFFu);
+          if (leader) mbar_arrive_expect_tx(&full_bar[slot], CG * C::kStageBytes);
+          tma_load_2d_cg<CG>(st, lo ? &tm_a_lo : &tm_a_hi, kk * kStageKBytes, m0, bar);
+          tma_load_2d_cg<CG>(st + kABytes, lo ? &tm_b_lo : &tm_b_hi, kk * kStageKBytes, n0, bar);
+          tma_load_3d_cg<CG>(st + kABytes + C::kBBytes, lo ? &maps.sfa_lo : &maps.sfa_hi, 0, chunk0, mgrp, bar);
+          tma_load_3d_cg<CG>(st + kABytes + C::kBBytes + C::kSfaBytes, lo ? &maps.sfb_lo : &maps.sfb_hi, 0, chunk0,
+                             tn * C::kSfGroups, bar);
+          gs += kProducers;
         }
+        ks -= k_stages;
+        tile += tile_step;
+        while (ks >= k_stages && tile < num_tiles) { ks -= k_stages; tile += tile_step; }
       }
     }
   } else if (warp == 1) {
@@ -232,8 +223,10 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
         tc_commit<CG>(smem_u32(bar));
         if constexpr (CG == 2) tc_commit<CG>(smem_u32(bar) + peer_off);
       };
-      int s = 0, as = 0, set = 0;
-      uint32_t phase = 0, aphase = 0, sphase = 0;
+      const uint64_t adesc0 = make_sw128_desc(smem_base), bdesc0 = make_sw128_desc(smem_base + kABytes);
+      const uint64_t sfdesc0 = make_sf_desc(smem_base + kABytes + C::kBBytes);
+      int s = 0, as = 0;
+      uint32_t phase = 0, aphase = 0, set = 0;
       bool ok = true;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         ok = CG == 2 ? mbar_wait_bounded_cluster(&acc_empty[as], aphase ^ 1, abort_flag)
@@ -243,31 +236,27 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
         const uint32_t d_tmem = tmem_base + as * BN;
         uint32_t accumulate = 0;
         for (int ks = 0; ks < k_stages; ++ks) {
-          ok = mbar_wait_bounded(&full_bar[s], phase, abort_flag);
-          if (ok && CG == 2) ok = mbar_wait_bounded_cluster(&peer_full[s], phase, abort_flag);
-          if constexpr (!SFCP) {
-            if (ok) ok = CG == 2 ? mbar_wait_bounded_cluster(&sf_ready[set], sphase, abort_flag)
-                                 : mbar_wait_bounded(&sf_ready[set], sphase, abort_flag);
-          }
+            ok = CG == 2 ? mbar_wait_bounded_cluster(&full_bar[s], phase, abort_flag)
+                       : mbar_wait_bounded(&full_bar[s], phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const bool lo = ks < g.lo_stages;
           const int kk = lo ? ks : ks - g.lo_stages;
           const uint32_t sfa_t = tmem_base + C::kSfCol0 + set * C::kSfSetCols, sfb_t = sfa_t + 16;
-          const uint64_t adesc = make_sw128_desc(smem_u32(stage_a(s))), bdesc = make_sw128_desc(smem_u32(stage_b(s)));
-          if constexpr (SFCP) {
-            // scale chunks shared -> tensor memory on this thread, ahead of the MMAs that read them
-            const uint32_t sfa_addr = smem_u32(stage_sfa(s)), sfb_addr = smem_u32(stage_sfb(s));
-            const int nchunk = lo ? min(4, g.lo_chunks - kk * 4) : 1;
-            for (int h = 0; h < nchunk; ++h) {
-              tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, make_sf_desc(sfa_addr + h * kSfChunk));
+          set ^= 1u;
+          const uint32_t soff = static_cast<uint32_t>(s) * (C::kStageBytes >> 4);   // in 16-byte units
+          const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff, sfa_d = sfdesc0 + soff;
+          const uint64_t sfb_d = sfa_d + (C::kSfaBytes >> 4);
+          const int nmma = lo ? min(4, g.lo_chunks - kk * 4) : min(4, (g.k_hi - kk * 128) / 32);
+          // scale chunks shared -> tensor memory, ahead of the MMAs that read them
+          const int nchunk = lo ? nmma : 1;
+          for (int h = 0; h < nchunk; ++h) {
+            tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, sfa_d + h * (kSfChunk >> 4));
 #pragma unroll
-              for (int q = 0; q < C::kSfGroups; ++q)
-                tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, make_sf_desc(sfb_addr + (q * 4 + h) * kSfChunk));
-            }
+            for (int q = 0; q < C::kSfGroups; ++q)
+              tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, sfb_d + (q * 4 + h) * (kSfChunk >> 4));
           }
           if (lo) {
-            const int nmma = min(4, g.lo_chunks - kk * 4);
             for (int h = 0; h < nmma; ++h) {
               // advance 32 bytes (64 E2M1) inside the swizzle span: +2 in the address field
               tc_mma_nvf4<CG>(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc_lo, sfa_t + 4 * h, sfb_t + (BN / 32) * h,
@@ -275,7 +264,6 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
               accumulate = 1;
             }
           } else {
-            const int nmma = min(4, (g.k_hi - kk * 128) / 32);
             for (int h = 0; h < nmma; ++h) {
               // scale id h selects byte h of every scale column; mirrored in the address' top bits
               const uint32_t idesc = idesc_hi | (static_cast<uint32_t>(h) << 4) | (static_cast<uint32_t>(h) << 29);
@@ -285,74 +273,11 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
             }
           }
           commit_all(&empty_bar[s]);                 // stage reusable once these MMAs have read it
-          if constexpr (!SFCP) commit_all(&sf_free[set]);   // and so is the set of scale columns
           if (++s == C::kStages) { s = 0; phase ^= 1; }
-          if (++set == kSfSets) { set = 0; sphase ^= 1; }
         }
         if (!ok) break;
         commit_all(&acc_full[as]);                   // accumulator complete (in both CTAs of a pair)
         if (++as == C::kAccStages) { as = 0; aphase ^= 1; }
-      }
-    } else if (elected && CG == 2) {
-      // ============ second CTA of a pair: tell the leader when a stage has landed here ============
-      const uint32_t remote = map_to_cta(smem_u32(peer_full), 0u);
-      int s = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        for (int ks = 0; ks < k_stages; ++ks) {
-          ok = mbar_wait_bounded(&full_bar[s], phase, abort_flag);
-          if (!ok) break;
-          mbar_arrive_cluster(remote + 8u * s);
-          if (++s == C::kStages) { s = 0; phase ^= 1; }
-        }
-      }
-    }
-  } else if (!SFCP && warp >= kLoaderWarp0 && warp < kLoaderWarp0 + 4) {
-    // ================================ scale loaders ================================
-    // Warp q fills lanes [32q, 32q+32) of the scale columns: lane i holds rows i, i+32, i+64, i+96 of
-    // a 128-row group, i.e. the 16 bytes at offset 16*i of a chunk are its four columns.
-    const int quad = warp & 3;
-    const uint32_t ready_addr = CG == 2 ? map_to_cta(smem_u32(sf_ready), 0u) : smem_u32(sf_ready);
-    int s = 0, set = 0;
-    uint32_t phase = 0, sphase = 0;
-    bool ok = true;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-      for (int ks = 0; ks < k_stages; ++ks) {
-        ok = mbar_wait_bounded_warp(&full_bar[s], phase, abort_flag);
-        if (ok) ok = mbar_wait_bounded_warp(&sf_free[set], sphase ^ 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t col = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + C::kSfCol0 + set * C::kSfSetCols;
-        const uint4* sfa = reinterpret_cast<const uint4*>(stage_sfa(s)) + lane;
-        const uint4* sfb = reinterpret_cast<const uint4*>(stage_sfb(s)) + lane;
-        uint32_t r[16];
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {               // A scales: columns 4h .. 4h+3
-          const uint4 v = sfa[h * 32];
-          r[4 * h] = v.x; r[4 * h + 1] = v.y; r[4 * h + 2] = v.z; r[4 * h + 3] = v.w;
-        }
-        tc_st_32x32b_x16(col, r);
-#pragma unroll
-        for (int half = 0; half < C::kSfGroups; ++half) {   // B scales: columns 16 + (BN/32) h + 4 q
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int idx = half * 4 + i;           // position in column order: h = idx / groups, q = idx % groups
-            const int h = idx / C::kSfGroups, q = idx % C::kSfGroups;
-            const uint4 v = sfb[(q * 4 + h) * 32];
-            r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
-          }
-          tc_st_32x32b_x16(col + 16 + half * 16, r);
-        }
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_cluster(ready_addr + 8u * set);   // scales of this stage are in tensor memory
-          mbar_arrive(&empty_bar[s]);                   // and no longer needed in shared memory
-        }
-        if (++s == C::kStages) { s = 0; phase ^= 1; }
-        if (++set == kSfSets) { set = 0; sphase ^= 1; }
       }
     }
   } else if (warp >= kFirstEpiWarp) {
@@ -372,19 +297,11 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN + cgp * C::kColsPerEpiWarp;
-      uint32_t packed[C::kColsPerEpiWarp / 2];
+      // all loads first, one wait: the accumulator is handed back after a single tensor-memory round trip
+      uint32_t r[C::kColsPerEpiWarp / 32][32];
 #pragma unroll
-      for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) {
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + c * 32, r);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          uint32_t d;
-          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(r[2 * i + 1])), "f"(__uint_as_float(r[2 * i])));
-          packed[c * 16 + i] = d;
-        }
-      }
+      for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) tc_ld_32x32b_x32(taddr + c * 32, r[c]);
+      tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(empty_addr + 8u * as);   // drained: the next tile may start
@@ -394,9 +311,15 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
 #pragma unroll
         for (int v = 0; v < C::kColsPerEpiWarp / 8; ++v) {
           const int col = col0 + v * 8;
-          if (col < g.n)
-            *reinterpret_cast<uint4*>(yrow + col) =
-                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          uint32_t d[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int cc = v * 8 + 2 * i;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;"
+                : "=r"(d[i])
+                : "f"(__uint_as_float(r[cc >> 5][(cc & 31) + 1])), "f"(__uint_as_float(r[cc >> 5][cc & 31])));
+          }
+          if (col < g.n) *reinterpret_cast<uint4*>(yrow + col) = make_uint4(d[0], d[1], d[2], d[3]);
         }
       }
     }
@@ -407,8 +330,8 @@ mixed_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_lo, const __grid_cons
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(g.status, PLQ_DEV_TIMEOUT);
     // give copies that are still in flight time to land before the shared memory is released
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) __nanosleep(1000);
     __syncthreads();
   }
   if constexpr (CG == 2) {          // the leader's MMAs read the peer's shared memory: leave together
@@ -453,25 +376,46 @@ static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t ro
   return r == CUDA_SUCCESS ? PLQ_OK : PLQ_ERR_TENSORMAP;
 }
 
-template <int BN, int CG, bool SFCP>
-static int launch_gemm(const void* a_lo, const void* a_hi, const void* b_lo, const void* b_hi, GemmArgs& g,
-                       cudaStream_t stream) {
-  using C = GemmCfg<BN, CG, SFCP>;
-  CUtensorMap tm_a_lo, tm_b_lo, tm_a_hi, tm_b_hi;
-  memset(&tm_a_lo, 0, sizeof(CUtensorMap)); memset(&tm_b_lo, 0, sizeof(CUtensorMap));
-  memset(&tm_a_hi, 0, sizeof(CUtensorMap)); memset(&tm_b_hi, 0, sizeof(CUtensorMap));
+// Tiled scale buffer as int32 [128 words, chunks per group, groups]; box = 4 chunks of `box_groups` groups.
+static int make_sf_tmap(CUtensorMap* tm, const void* base, int64_t chunks, int64_t groups, int box_groups) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return PLQ_ERR_TENSORMAP;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(chunks), static_cast<cuuint64_t>(groups)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kSfChunk), static_cast<cuuint64_t>(chunks) * kSfChunk};
+  const cuuint32_t box[3] = {128, 4, static_cast<cuuint32_t>(box_groups)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? PLQ_OK : PLQ_ERR_TENSORMAP;
+}
+
+struct GemmPtrs {
+  const void *a_lo, *a_lo_sf, *a_hi, *a_hi_sf, *b_lo, *b_lo_sf, *b_hi, *b_hi_sf;
+};
+
+template <int BN, int CG>
+static int launch_gemm(const GemmPtrs& p, GemmArgs& g, cudaStream_t stream) {
+  using C = GemmCfg<BN, CG>;
+  GemmMaps tm;
+  memset(&tm, 0, sizeof(tm));
+  const int64_t mg = (g.m + 127) / 128, ng = (g.n + 127) / 128;
   int st;
   if (g.k_lo) {
-    if ((st = make_tmap(&tm_a_lo, a_lo, g.m, g.k_lo / 2, kBM)) != PLQ_OK) return st;
-    if ((st = make_tmap(&tm_b_lo, b_lo, g.n, g.k_lo / 2, C::kBRows)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm.a_lo, p.a_lo, g.m, g.k_lo / 2, kBM)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm.b_lo, p.b_lo, g.n, g.k_lo / 2, C::kBRows)) != PLQ_OK) return st;
+    if ((st = make_sf_tmap(&tm.sfa_lo, p.a_lo_sf, g.lo_chunks, mg, 1)) != PLQ_OK) return st;
+    if ((st = make_sf_tmap(&tm.sfb_lo, p.b_lo_sf, g.lo_chunks, ng, C::kSfGroups)) != PLQ_OK) return st;
   }
   if (g.k_hi) {
-    if ((st = make_tmap(&tm_a_hi, a_hi, g.m, g.k_hi, kBM)) != PLQ_OK) return st;
-    if ((st = make_tmap(&tm_b_hi, b_hi, g.n, g.k_hi, C::kBRows)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm.a_hi, p.a_hi, g.m, g.k_hi, kBM)) != PLQ_OK) return st;
+    if ((st = make_tmap(&tm.b_hi, p.b_hi, g.n, g.k_hi, C::kBRows)) != PLQ_OK) return st;
+    if ((st = make_sf_tmap(&tm.sfa_hi, p.a_hi_sf, g.hi_chunks, mg, 1)) != PLQ_OK) return st;
+    if ((st = make_sf_tmap(&tm.sfb_hi, p.b_hi_sf, g.hi_chunks, ng, C::kSfGroups)) != PLQ_OK) return st;
   }
   g.tiles_m = (g.m + kBM * CG - 1) / (kBM * CG);
   g.tiles_n = (g.n + BN - 1) / BN;
-  auto kernel = mixed_gemm_kernel<BN, CG, SFCP>;
+  auto kernel = mixed_gemm_kernel<BN, CG>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   PLQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -495,7 +439,7 @@ static int launch_gemm(const void* a_lo, const void* a_hi, const void* b_lo, con
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm_a_lo, tm_b_lo, tm_a_hi, tm_b_hi, g));
+  PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm, g));
   return PLQ_OK;
 }
 
@@ -520,8 +464,7 @@ extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_s
   int st = device_check();
   if (st != PLQ_OK) return st;
   GemmArgs g;
-  g.a_lo_sf = static_cast<const uint8_t*>(a_lo_sf); g.a_hi_sf = static_cast<const uint8_t*>(a_hi_sf);
-  g.b_lo_sf = static_cast<const uint8_t*>(b_lo_sf); g.b_hi_sf = static_cast<const uint8_t*>(b_hi_sf);
+  const GemmPtrs ptrs = {a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf};
   g.y = static_cast<__nv_bfloat16*>(y_bf16);
   g.ldy = ldy;
   g.status = dev_status;
@@ -531,8 +474,6 @@ extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_s
   g.hi_chunks = static_cast<int>((k_hi + 127) / 128);
   g.lo_stages = (g.lo_chunks + 3) / 4;
   g.hi_stages = g.hi_chunks;
-  g.m_sf_groups = static_cast<int>((m + 127) / 128);
-  g.n_sf_groups = static_cast<int>((n + 127) / 128);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (variant == PLQ_GEMM_AUTO) {
     // A CTA pair needs 30 % fewer bytes from L2 per MMA, which is what bounds large problems;
@@ -544,11 +485,9 @@ extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_s
     else if (n >= 256 && (wide_tiles >= sms || n % 256 == 0)) variant = PLQ_GEMM_128x256;
     else variant = PLQ_GEMM_128x128;
   }
-  if (variant == PLQ_GEMM_128x128) return launch_gemm<128, 1, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
-  if (variant == PLQ_GEMM_128x256) return launch_gemm<256, 1, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
-  if (variant == PLQ_GEMM_PAIR_256x256) return launch_gemm<256, 2, true>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
-  if (variant == 12) return launch_gemm<256, 1, false>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
-  if (variant == 13) return launch_gemm<256, 2, false>(a_lo_codes, a_hi_codes, b_lo_codes, b_hi_codes, g, s);
+  if (variant == PLQ_GEMM_128x128) return launch_gemm<128, 1>(ptrs, g, s);
+  if (variant == PLQ_GEMM_128x256) return launch_gemm<256, 1>(ptrs, g, s);
+  if (variant == PLQ_GEMM_PAIR_256x256) return launch_gemm<256, 2>(ptrs, g, s);
   return PLQ_ERR_SHAPE;
 }
 

@@ -133,7 +133,7 @@ def _check_pair(a: PackedMatrix, b: PackedMatrix, layout: int) -> None:
         raise ValueError("scale buffers are in the wrong layout for this kernel")
 
 
-GEMM_VARIANTS = {None: 0, "auto": 0, "128x128": 1, "128x256": 2, "pair256x256": 3, "128x256-st": 12, "pair256x256-st": 13}
+GEMM_VARIANTS = {None: 0, "auto": 0, "128x128": 1, "128x256": 2, "pair256x256": 3}
 
 
 def mixed_gemm(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
