@@ -135,12 +135,17 @@ PLQ_API int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_sf, 
 
 /*
  * Decode GEMV, m <= 8: same contract as plq_mixed_gemm but streaming the weights once from
- * HBM with 128-bit loads; scale buffers of both operands in PLQ_SF_ROWMAJOR layout.
+ * HBM; scale buffers of both operands in PLQ_SF_ROWMAJOR layout.
+ * `workspace` (device memory, 16-byte aligned, at least plq_gemv_workspace_bytes(n) bytes, zeroed
+ * once by the caller and left zeroed by every call) lets the kernel cut K into slices whose
+ * partial sums it combines in a fixed order; calls that share a workspace must not overlap on
+ * the GPU.  With workspace == NULL only shapes that need no K slicing are accepted.
  */
+PLQ_API int64_t plq_gemv_workspace_bytes(int64_t n);
 PLQ_API int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
              const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
              int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
-             void* y_bf16, int64_t ldy, void* stream);
+             void* y_bf16, int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

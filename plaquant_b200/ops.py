@@ -152,13 +152,32 @@ def mixed_gemm(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = N
     return y
 
 
-def gemv(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+_gemv_ws = {}
+
+
+def gemv_workspace(device, n: int) -> torch.Tensor:
+    """Per (device, stream) zero-initialised scratch for the GEMV's K-slice reduction; grown on demand.
+    Calls on one stream are ordered, so they can share it."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    need = _lib.lib().plq_gemv_workspace_bytes(n)
+    ws = _gemv_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=f"cuda:{key[0]}")
+        _gemv_ws[key] = ws
+    return ws
+
+
+def gemv(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
+         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode path, a.rows <= 8 (row-major scale layout)."""
     _check_pair(a, b, SF_ROWMAJOR)
     y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
+    ws = workspace if workspace is not None else gemv_workspace(a.device, b.rows)
     with torch.cuda.device(a.device):
         st = _lib.lib().plq_gemv(_ptr(a.lo_codes), _ptr(a.lo_sf), _ptr(a.hi_codes), _ptr(a.hi_sf),
                                  _ptr(b.lo_codes), _ptr(b.lo_sf), _ptr(b.hi_codes), _ptr(b.hi_sf),
-                                 a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0), _stream(a.device))
+                                 a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0), _ptr(ws), ws.numel(),
+                                 _stream(a.device))
     _lib.check(st)
     return y

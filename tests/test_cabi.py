@@ -51,7 +51,7 @@ def test_argument_checks_run_before_any_device_work(lib):
     assert lib.plq_pack(None, 4, 256, 64, 0, p16, p16, p16, p16, 0, None) == -1
     assert lib.plq_pack(p16 + 2, 4, 256, 64, 0, p16, p16, p16, p16, 0, None) == -3
     assert lib.plq_rmsnorm_pack(p16, None, 1e-6, 4, 256, 64, 1, p16, p16, p16, p16, 0, None) == -1
-    assert lib.plq_gemv(p16, p16, p16, p16, p16, p16, p16, p16, 9, 64, 192, 64, p16, 64, None) == -2
+    assert lib.plq_gemv(p16, p16, p16, p16, p16, p16, p16, p16, 9, 64, 192, 64, p16, 64, None, 0, None) == -2
     assert lib.plq_mixed_gemm(p16, p16, p16, p16, p16, p16, p16, p16, 16, 12, 192, 64, p16, 16, p16, None) == -2
     assert lib.plq_mixed_gemm(p16, p16, p16, p16, p16, p16, p16, p16, 16, 16, 192, 64, p16, 16, None, None) == -1
 
