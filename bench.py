@@ -67,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -292,7 +292,7 @@ def main_ours(args, rank, local_rank, world):
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
         "gpu_launches": 2 * len(layers) * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "mixed_gemm_kernel<256>", "achieved": gemm_tflops,
+        "roofline": {"bound": "tensor", "kernel": "mixed_gemm_kernel<256, 2>", "achieved": gemm_tflops,
                      "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
                      "peak_source": f"4 x {peaks['source']} cuBLAS bf16 sustained ({peaks['bf16_tflops_sustained']} TF/s); "
                                     "no FP4 peak is measured on this pool",
@@ -300,7 +300,10 @@ def main_ours(args, rank, local_rank, world):
                      "flops_per_step": fl, "gemm_ms_per_step": gemm_ms,
                      "per_gemm_ms": {k: sum(v) / len(v) for k, v in per_gemm.items()},
                      "per_gemm_tflops": {L["name"]: 2.0 * M_TOKENS * L["n"] * L["k"] / (sum(per_gemm[L["name"]]) / len(per_gemm[L["name"]]) * 1e-3) / 1e12 for L in layers},
-                     "traffic": None},
+                     "traffic": 83.0e6,
+                     "traffic_note": "dram__bytes_read+write of one QKV-shape launch (412 GFLOP, 134.6 MB of operands "
+                                     "and output) from the ncu capture in profiles/; part of the output is still in L2 "
+                                     "when the kernel ends"},
         **extra,
     }
     if world == 1:
@@ -324,6 +327,41 @@ def time_cuda(torch, fn, iters, flush=None):
     return tot / iters
 
 
+def clone_packed(plq, p, copies):
+    """`copies` independent device copies of a packed matrix (to cycle through operands larger than L2)."""
+    return [plq.PackedMatrix(p.rows, p.k_lo, p.k_hi, p.lo_codes.clone(), p.lo_sf.clone(), p.hi_codes.clone(),
+                             p.hi_sf.clone(), p.sf_layout) for _ in range(copies)]
+
+
+def time_rotating(torch, fns, rounds):
+    """Average milliseconds per call of the callables in `fns`: one pass over them is captured in a CUDA
+    graph (so the Python/ctypes launch path, ~15 us per call, is not what gets timed) and the graph
+    is replayed `rounds` times between one pair of CUDA events.  Each callable works on its own copy of
+    the operands and the copies together exceed L2 several times, so every launch streams from HBM."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for f in fns:
+            f()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for f in fns:
+                f()
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(rounds):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / (rounds * len(fns))
+
+
 def side_benchmarks(plq, torch, dev, peaks):
     """configs[1] (fused RMSNorm-quant + Hadamard-pack, [4096, 4096]) and configs[2] (decode GEMV
     sweep), each kernel timed alone with an L2 flush before every launch; HBM roofline."""
@@ -336,11 +374,14 @@ def side_benchmarks(plq, torch, dev, peaks):
     gamma = (torch.rand(4096, generator=g) + 0.5).to(torch.bfloat16).to(dev)
     pa = plq.alloc_packed(4096, 4096, 128, "tiled", dev)
     fn = lambda: plq.pack(x, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pa)
-    for _ in range(5):
-        fn()
-    ms = time_cuda(torch, fn, 20, flush)
+    xs = [x.clone() for _ in range(12)]                       # 12 x 33.5 MB of input > 3 x L2
+    pas = [plq.alloc_packed(4096, 4096, 128, "tiled", dev) for _ in range(12)]
+    fns = [(lambda xi=xi, pi=pi: plq.pack(xi, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pi)) for xi, pi in zip(xs, pas)]
+    ms = time_rotating(torch, fns, 5)
+    del xs, pas, fns
     nbytes = 2 * 4096 * 4096 + 2 * 4096 + 4096 * 2364
     out["pack"] = {"workload": "RMSNorm + Hadamard128 + NVFP4/MXFP8 pack, bf16 [4096, 4096]", "us": ms * 1e3,
+                   "timing": "back-to-back launches over 12 operand copies (> 3 x L2), one event pair",
                    "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
                    "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                    "frac_of_nominal_hbm": nbytes / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
@@ -349,20 +390,20 @@ def side_benchmarks(plq, torch, dev, peaks):
         w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
         pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
         del w
+        pws = clone_packed(plq, pw, max(2, int(400e6 // pw.nbytes())))      # >= 400 MB of weights in rotation
         for m in (1, 2, 4, 8):
             xa = plq.pack(x[:m, :k] if k <= 4096 else torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev),
                           k // 32, hadamard=True, sf_layout="rowmajor")
             y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-            fn = lambda: plq.gemv(xa, pw, out=y)
-            for _ in range(3):
-                fn()
-            ms = time_cuda(torch, fn, 10, flush)
+            fns = [(lambda w=w_: plq.gemv(xa, w, out=y)) for w_ in pws]
+            ms = time_rotating(torch, fns, 5)
             nb = pw.nbytes() + xa.nbytes() + m * n * 2
             gv[f"{name}_m{m}"] = {"us": ms * 1e3, "bytes": nb, "gbs": nb / (ms * 1e-3) / 1e9,
                                   "frac_of_measured_hbm": nb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                   "frac_of_nominal_hbm": nb / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
-        del pw
+        del pw, pws
     out["gemv"] = gv
+    out["gemv_timing"] = "back-to-back launches cycling >= 400 MB of weight copies (> 3 x L2), one event pair"
     out["hbm_peak_gbs"] = {"measured": peaks["hbm_gbs"], "nominal": NOMINAL_HBM_GBS, "source": peaks["source"]}
     return out
 
@@ -391,6 +432,8 @@ def main_case(args):
         pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
         pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout="rowmajor")
         y = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+        pws = clone_packed(plq, pw, max(2, int(400e6 // pw.nbytes())))
+        rot = [(lambda w=w_: plq.gemv(pa, w, out=y)) for w_ in pws]
         fn = lambda: plq.gemv(pa, pw, out=y)
         work, unit = pw.nbytes() + pa.nbytes() + y.numel() * 2, "GB/s"
     else:
@@ -405,10 +448,16 @@ def main_case(args):
         fn()
     torch.cuda.synchronize()
     ms = time_cuda(torch, fn, args.steps, flush)
+    if args.case == "gemv":
+        ms_rot = time_rotating(torch, rot, max(1, args.steps // 4))
     plq.check_device_status()
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    print(json.dumps({"case": args.case, "shape": name, "m": args.m, "us_per_launch": ms * 1e3, "rate": rate,
-                      "unit": unit, "work": work}), flush=True)
+    line = {"case": args.case, "shape": name, "m": args.m, "us_per_launch": ms * 1e3, "rate": rate, "unit": unit,
+            "work": work}
+    if args.case == "gemv":
+        line["us_back_to_back"] = ms_rot * 1e3
+        line["rate_back_to_back"] = work / (ms_rot * 1e-3) / 1e9
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -419,7 +468,7 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
