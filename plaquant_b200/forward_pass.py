@@ -1,0 +1,167 @@
+"""Llama-architecture forward with the mixed NVFP4 / MXFP8 linears, in the shape of the reference's
+`IndependentResQForward` (inference/forward_pass.py:118-319 in the reference): norm -> q,k,v ->
+RoPE -> attention -> o_proj -> norm -> gate, up -> silu * up -> down_proj, LM head unquantised.
+
+What runs where.  The hot path of this repository - RMSNorm + rotation + quantise-and-pack and the
+quantised linears - runs on the CUDA library (fused: the two RMSNorms of a layer never produce a
+bf16 tensor, they feed the pack kernel).  Everything the reference also leaves to PyTorch stays in
+PyTorch: embedding, RoPE, scaled-dot-product attention (forward_pass.py:249 there), SiLU, residual
+adds, the final norm and the LM head (forward_pass.py:178-181 there).
+
+Tensor parallelism (Megatron): QKV and gate_up are column-parallel (N sharded by heads / by FFN
+columns, no exchange), O and down are row-parallel (K sharded, one all-reduce each), see tp.py.
+Weights are random-initialised per layer from a seed (no checkpoints are available offline).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import ops, tp
+from .quantize import QuantizedLinear
+from .rotation import get_hadamard_matrix  # noqa: F401  (re-exported, as the reference module does)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """Stand-alone RMSNorm with the reference's arithmetic (forward_pass.py:33-39): float32, one cast.
+    Only used off the hot path (final norm before the unquantised LM head)."""
+    dtype = x.dtype
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (weight.float() * xf).to(dtype)
+
+
+def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, k_hi: int, hadamard: bool = True,
+                   sf_layout: str = "tiled") -> ops.PackedMatrix:
+    """Fused RMSNorm -> block-Hadamard(128) -> NVFP4 | MXFP8 pack: what a quantised linear consumes."""
+    return ops.pack(x, k_hi, hadamard=hadamard, sf_layout=sf_layout, gamma=weight, eps=eps)
+
+
+@dataclass
+class LlamaConfig:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-6
+    high_fraction: float = 1.0 / 32
+
+    @classmethod
+    def llama3_70b(cls):
+        return cls(8192, 28672, 80, 64, 8, 128, 128256)
+
+    @classmethod
+    def llama3_8b(cls):
+        return cls()
+
+
+class _Layer:
+    __slots__ = ("ln1", "ln2", "qkv", "o", "gate_up", "down")
+
+
+class ResQForwardB200:
+    """Decoder stack with packed weights resident on one GPU (one tensor-parallel rank)."""
+
+    def __init__(self, cfg: LlamaConfig, device, ctx: Optional[tp.TPContext] = None, seed: int = 0,
+                 num_layers: Optional[int] = None):
+        self.cfg, self.device, self.ctx = cfg, torch.device(device), ctx or tp.TPContext()
+        c, r, s = cfg, self.ctx.rank, self.ctx.size
+        assert c.num_heads % s == 0 and c.num_kv_heads % s == 0 and c.intermediate_size % (s * 128) == 0
+        self.heads, self.kv_heads = c.num_heads // s, c.num_kv_heads // s
+        self.ffn = c.intermediate_size // s
+        self.k_hi_hidden = tp.outlier_count(c.hidden_size, c.high_fraction)
+        self.k_hi_attn = tp.outlier_count(self.heads * c.head_dim, c.high_fraction)     # rank-local K of o_proj
+        self.k_hi_ffn = tp.outlier_count(self.ffn, c.high_fraction)                     # rank-local K of down_proj
+        self.layers: List[_Layer] = []
+        n_layers = c.num_layers if num_layers is None else num_layers
+        for li in range(n_layers):
+            g = torch.Generator(device=self.device).manual_seed(seed * 100003 + li * 16 + r)
+            L = _Layer()
+            L.ln1 = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
+            L.ln2 = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
+            L.qkv = self._linear((self.heads + 2 * self.kv_heads) * c.head_dim, c.hidden_size, self.k_hi_hidden, g)
+            L.o = self._linear(c.hidden_size, self.heads * c.head_dim, self.k_hi_attn, g)
+            L.gate_up = self._linear(2 * self.ffn, c.hidden_size, self.k_hi_hidden, g)
+            L.down = self._linear(c.hidden_size, self.ffn, self.k_hi_ffn, g)
+            self.layers.append(L)
+        g = torch.Generator(device=self.device).manual_seed(seed * 100003 + 999983)      # replicated on every rank
+        self.embed = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+        self.final_norm = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
+        self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+        self.kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        self.pos = 0
+
+    def _linear(self, n: int, k: int, k_hi: int, g: torch.Generator) -> QuantizedLinear:
+        """Random N(0, 0.02) weight [n, k], rotated and packed on the device; only the packed form is kept."""
+        w = (torch.randn(n, k, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+        p = ops.pack(w, k_hi, hadamard=True, sf_layout="rowmajor")
+        del w
+        return QuantizedLinear(p.lo_codes, p.lo_sf, p.hi_codes, p.hi_sf, online_had=True)
+
+    # ---- pieces ----------------------------------------------------------------------------------
+    def _quantized_linear(self, x, lin: QuantizedLinear, norm_weight=None):
+        """[RMSNorm] -> Hadamard -> quantise -> packed GEMM / GEMV (reference: forward_pass.py:278-319)."""
+        return lin(x, norm_weight=norm_weight, eps=self.cfg.rms_eps)
+
+    def _rope(self, q, k, pos0: int):
+        c = self.cfg
+        t = q.shape[1]
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=q.device, dtype=torch.float32) / c.head_dim))
+        ang = torch.outer(torch.arange(pos0, pos0 + t, device=q.device, dtype=torch.float32), inv)
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1)[None, :, None, :], torch.cat([ang.sin(), ang.sin()], -1)[None, :, None, :]
+
+        def rot(v):
+            v1, v2 = v[..., : c.head_dim // 2], v[..., c.head_dim // 2:]
+            return (v.float() * cos + torch.cat([-v2, v1], -1).float() * sin).to(v.dtype)
+        return rot(q), rot(k)
+
+    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int) -> torch.Tensor:
+        c, L = self.cfg, self.layers[li]
+        b, t, _ = h.shape
+        qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
+        q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
+        q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
+        q, k = self._rope(q, k, pos0)
+        if pos0 == 0:
+            self.kv[li] = (k, v)
+        else:
+            self.kv[li] = (torch.cat([self.kv[li][0], k], 1), torch.cat([self.kv[li][1], v], 1))
+        kk, vv = self.kv[li]
+        attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                              is_causal=(t > 1), enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
+        h = h + self.ctx.all_reduce(self._quantized_linear(attn, L.o))
+        gu = self._quantized_linear(h, L.gate_up, norm_weight=L.ln2)
+        act = F.silu(gu[..., : self.ffn]) * gu[..., self.ffn:]
+        return h + self.ctx.all_reduce(self._quantized_linear(act, L.down))
+
+    # ---- public ----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, input_ids: torch.Tensor, pos0: int = 0) -> torch.Tensor:
+        """input_ids [B, T] -> logits of the last position [B, vocab] (float32)."""
+        if pos0 == 0:
+            self.kv = [None] * len(self.layers)
+        h = F.embedding(input_ids, self.embed)
+        for li in range(len(self.layers)):
+            h = self._forward_layer(li, h, pos0)
+        self.pos = pos0 + input_ids.shape[1]
+        last = rms_norm(h[:, -1], self.final_norm, self.cfg.rms_eps)
+        return last.float() @ self.lm_head.float().T
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, steps: int) -> torch.Tensor:
+        """Prefill + `steps` greedy decode steps; returns the generated ids [B, steps]."""
+        out = []
+        nxt = self.forward(input_ids).argmax(-1, keepdim=True)
+        for _ in range(steps):
+            out.append(nxt)
+            nxt = self.forward(nxt, pos0=self.pos).argmax(-1, keepdim=True)
+        return torch.cat(out, 1)

@@ -48,3 +48,18 @@ def fused_mixed_gemm(A_main: torch.Tensor, B_main: torch.Tensor, A_high: Optiona
 
 # the reference exports five numbered variants of the same fused operation with identical signatures
 fused_mixed_gemm_v2 = fused_mixed_gemm_v3 = fused_mixed_gemm_v4 = fused_mixed_gemm_v5 = fused_mixed_gemm
+
+
+# `plaquant_b200.mixed_gemm` is both this module (the reference's module name) and, at package level,
+# the packed-operand GEMM function; importing the module must not hide the function, so the module
+# object itself is callable and forwards to it.
+import sys as _sys
+import types as _types
+
+
+class _CallableModule(_types.ModuleType):
+    def __call__(self, *args, **kwargs):
+        return ops.mixed_gemm(*args, **kwargs)
+
+
+_sys.modules[__name__].__class__ = _CallableModule

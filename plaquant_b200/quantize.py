@@ -67,10 +67,11 @@ class QuantizedLinear:
     def from_weight(cls, weight: torch.Tensor, high_fraction: float = 1.0 / 32, rotate: bool = True,
                     online_had: bool = True) -> "QuantizedLinear":
         """Round-to-nearest quantisation of W[N, K] (bf16, CUDA) on the device; the last
-        int(high_fraction * K) input channels become the MXFP8 subspace, the block-Hadamard(128)
+        ~high_fraction * K input channels (tp.outlier_count) become the MXFP8 subspace, the block-Hadamard(128)
         rotation is applied along K first when `rotate` (promix/quantize/rotation.py:100-116)."""
         k = weight.shape[1]
-        k_hi = int(high_fraction * k)
+        from .tp import outlier_count
+        k_hi = outlier_count(k, high_fraction)   # int(high_fraction * K), rounded up to the kernels' granularity
         p = ops.pack(weight, k_hi, hadamard=rotate, sf_layout="rowmajor")
         return cls(p.lo_codes, p.lo_sf, p.hi_codes if k_hi else None, p.hi_sf if k_hi else None,
                    online_had=online_had)

@@ -1,0 +1,98 @@
+"""The reference-shaped Python API (QuantizedLinear, fused_mixed_gemm, installers, the decoder
+forward) on top of the C ABI, checked against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from tests._util import f32_of, rel_l2, synth_activation, synth_gamma, synth_weight
+
+pytestmark = pytest.mark.gpu
+plq = pytest.importorskip("plaquant_b200")
+
+
+def _oracle_linear(x, w, k_hi, gamma=None):
+    px = F.prepare_activation(f32_of(x), k_hi, gamma=None if gamma is None else f32_of(gamma), eps=1e-6, hadamard=True)
+    pw = F.prepare_activation(f32_of(w), k_hi, hadamard=True)
+    return F.round_to_bf16(F.linear(px, pw))
+
+
+@pytest.mark.parametrize("rows", [4, 200])
+@pytest.mark.parametrize("norm", [False, True])
+def test_quantized_linear_matches_oracle(rows, norm):
+    from plaquant_b200.quantize import QuantizedLinear
+    k, n = 1024, 384
+    x, w = synth_activation(rows, k, seed=rows), synth_weight(n, k, seed=9)
+    gamma = synth_gamma(k, seed=3) if norm else None
+    lin = QuantizedLinear.from_weight(w.cuda(), high_fraction=1 / 32)
+    assert (lin.in_features, lin.out_features, lin.high_bits_length, lin.gemm_impl) == (k, n, 64, "b200")
+    y = lin(x.cuda().view(2, rows // 2, k), norm_weight=None if gamma is None else gamma.cuda())
+    assert y.shape == (2, rows // 2, n) and y.dtype == torch.bfloat16
+    plq.check_device_status()
+    assert rel_l2(f32_of(y).reshape(rows, n), _oracle_linear(x, w, 64, gamma)) <= 1e-3
+    with pytest.raises(NotImplementedError):
+        lin.set_kernel("pytorch")              # the reference's fallback does not exist here
+    cpu = QuantizedLinear(lin.w_main_int.cpu(), lin.w_main_scale.cpu(), lin.w_high_int.cpu(), lin.w_high_scale.cpu(),
+                          online_had=True)
+    with pytest.raises(RuntimeError):
+        cpu(x)                                 # weights not on a GPU: loud error, no CPU path
+    y2 = cpu.to("cuda")(x.cuda(), norm_weight=None if gamma is None else gamma.cuda())
+    assert torch.equal(y2, y.view(rows, n))
+
+
+def test_fused_mixed_gemm_call_shape():
+    from plaquant_b200.mixed_gemm import fused_mixed_gemm
+    x, w = synth_activation(130, 512, seed=1), synth_weight(264, 512, seed=2)
+    pa = plq.pack(x.cuda(), 64, hadamard=True, sf_layout="tiled")
+    pb = plq.pack(w.cuda(), 64, hadamard=True, sf_layout="tiled")
+    y = fused_mixed_gemm(pa.lo_codes.view(2, 65, -1), pb.lo_codes, pa.hi_codes, pb.hi_codes, pa.lo_sf, pb.lo_sf,
+                         None, None, pa.hi_sf, pb.hi_sf, None, None)
+    assert y.shape == (2, 65, 264)
+    assert torch.equal(y.view(130, 264), plq.mixed_gemm(pa, pb))
+    with pytest.raises(ValueError):
+        fused_mixed_gemm(pa.lo_codes, pb.lo_codes, pa.hi_codes, pb.hi_codes, pa.lo_sf, pb.lo_sf, torch.zeros(1), None,
+                         pa.hi_sf, pb.hi_sf)
+
+
+def test_install_real_forward_on_a_module_tree():
+    from plaquant_b200 import real_forward
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512, bias=False), torch.nn.SiLU(),
+                                torch.nn.Linear(512, 128, bias=False)).cuda().to(torch.bfloat16)
+    x = synth_activation(32, 256, seed=4).cuda()
+    ref = model(x).float()
+    real_forward.init_kernel()
+    assert real_forward.install_real_forward(model, high_fraction=1 / 8) == 2
+    y = model(x).float()
+    cos = torch.nn.functional.cosine_similarity(y.flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.97, cos                     # 4-bit weights and activations against the bf16 model
+
+
+def test_hadamard_matrix_and_decoder_forward():
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200, rms_norm_quant
+    from plaquant_b200.rotation import get_hadamard_matrix, is_block_hadamard
+    h = get_hadamard_matrix(128)
+    assert torch.allclose(h @ h.T, torch.eye(128), atol=1e-5) and is_block_hadamard(h)
+    assert torch.equal(torch.sign(h[1]), torch.tensor([1.0, -1.0] * 64))           # Sylvester order
+    x = synth_activation(16, 256, seed=8)
+    rot = (x.float().view(16, 2, 128) @ h).view(16, 256)
+    assert rel_l2(F.block_hadamard_det(f32_of(x)), F.round_to_bf16(rot.numpy())) < 2e-3
+    gamma = synth_gamma(256, 2)
+    p = rms_norm_quant(x.cuda(), gamma.cuda(), 1e-6, 64, sf_layout="rowmajor")
+    want = F.prepare_activation(f32_of(x), 64, gamma=f32_of(gamma), eps=1e-6)
+    assert np.array_equal(p.lo_codes.cpu().numpy(), want["lo_codes"])
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      vocab_size=1000)
+    model = ResQForwardB200(cfg, "cuda", seed=1)
+    ids = torch.randint(0, 1000, (3, 40), generator=torch.Generator().manual_seed(0)).cuda()
+    logits = model.forward(ids)
+    assert logits.shape == (3, 1000) and torch.isfinite(logits).all()
+    assert torch.equal(logits, model.forward(ids))
+    gen = model.generate(ids, 5)
+    assert gen.shape == (3, 5)
+    # incremental decoding reproduces a full forward over the extended sequence
+    full = model.forward(torch.cat([ids, gen[:, :1]], 1))
+    model.forward(ids)
+    step = model.forward(gen[:, :1], pos0=40)
+    assert rel_l2(step.cpu().numpy(), full.cpu().numpy()) < 0.05
+    plq.check_device_status()

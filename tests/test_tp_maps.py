@@ -1,0 +1,114 @@
+"""Tensor-parallel partition maps and the reduce algebra, on CPU ranks (gloo, world size 2),
+with the CPU oracle standing in for the kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import formats as F
+from plaquant_b200 import tp
+from tests._util import bits_of, synth_activation, synth_weight
+
+
+def test_outlier_count_respects_kernel_granularity():
+    for k, want in ((4096, 128), (14336, 448), (8192, 256), (28672, 896), (1024, 64), (3584, 128), (128, 64)):
+        k_hi = tp.outlier_count(k)
+        assert k_hi == want, (k, k_hi)
+        assert k_hi % 32 == 0 and (k - k_hi) % 64 == 0 and k_hi >= k / 32
+    # the 70B shapes at every tensor-parallel degree
+    for size in (1, 2, 4, 8):
+        for k in (8192, 28672):
+            for r in range(size):
+                s = tp.row_parallel_cols(k, r, size)
+                assert (s.stop - s.start) % 128 == 0
+                tp.outlier_count(s.stop - s.start)
+        for n in (10240, 57344):
+            assert sum(tp.column_parallel_rows(n, r, size).stop - tp.column_parallel_rows(n, r, size).start
+                       for r in range(size)) == n
+    with pytest.raises(ValueError):
+        tp.row_parallel_cols(4096 + 128, 0, 8)
+
+
+def _f32(t):
+    return F.bf16_bits_to_f32(bits_of(t))
+
+
+def _partial(x, w, ks: slice):
+    xs, ws = _f32(x)[:, ks], _f32(w)[:, ks]
+    k_hi = tp.outlier_count(ks.stop - ks.start)
+    return F.linear(F.prepare_activation(xs, k_hi, hadamard=True), F.prepare_activation(ws, k_hi, hadamard=True))
+
+
+def _worker(rank, size, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=size)
+    try:
+        ctx = tp.TPContext.from_env()
+        x, w = synth_activation(4, 512, seed=5), synth_weight(48, 512, seed=6)
+        # row-parallel: own K shard, partial product, one all-reduce
+        y = torch.from_numpy(_partial(x, w, tp.row_parallel_cols(512, rank, size)))
+        ctx.all_reduce(y)
+        # column-parallel: own N shard, no exchange (gathered here only to check it)
+        rows = tp.column_parallel_rows(48, rank, size)
+        k_hi = tp.outlier_count(512)
+        yc = torch.from_numpy(F.linear(F.prepare_activation(_f32(x), k_hi, hadamard=True),
+                                       F.prepare_activation(_f32(w)[rows], k_hi, hadamard=True)))
+        parts = [torch.empty_like(yc) for _ in range(size)]
+        dist.all_gather(parts, yc)
+        if rank == 0:
+            out.put((y.numpy(), torch.cat(parts, 1).numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_and_column_parallel_on_two_gloo_ranks():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    y_row, y_col = out.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    x, w = synth_activation(4, 512, seed=5), synth_weight(48, 512, seed=6)
+    want_row = _partial(x, w, slice(0, 256)) + _partial(x, w, slice(256, 512))
+    assert np.array_equal(y_row, want_row)                      # same partials, same sum
+    k_hi = tp.outlier_count(512)
+    want_col = F.linear(F.prepare_activation(_f32(x), k_hi, hadamard=True), F.prepare_activation(_f32(w), k_hi, hadamard=True))
+    assert np.array_equal(y_col, want_col)                      # N shards are independent rows of W
+    # the sharded product is a different (rank-local) quantisation of the same linear map
+    full = _f32(x) @ _f32(w).T
+    assert np.linalg.norm(want_row - full) / np.linalg.norm(full) < 0.2
+
+
+def test_rank_that_fails_before_the_collective_is_reported():
+    """Host-side failure injection: a rank that raises never joins; the other must not hang forever."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_failing_pair, args=(q,))
+    p.start()
+    p.join(90)
+    assert p.exitcode == 0
+    assert q.get(timeout=5) == "timeout-detected"
+
+
+def _failing_pair(q):
+    import datetime
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    # world of 2 in which rank 1 never shows up: initialisation must time out, not hang
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=5))
+        q.put("unexpected-success")
+    except Exception:
+        q.put("timeout-detected")
