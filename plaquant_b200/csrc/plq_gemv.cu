@@ -312,10 +312,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
   }
 }
 
-// Workspace layout: [tiles] uint32 tickets (padded to 256 bytes), then [8][tiles][16][8] float32 partial sums.
-static int64_t gemv_ws_bytes(int64_t n) {
-  const int64_t tiles = (n + 15) / 16;
-  return ((tiles * 4 + 255) / 256) * 256 + 8 * tiles * 128 * 4;
+// Workspace layout: uint32 tickets, then [8][tiles][16][8] float32 partial sums.  The ticket area is sized
+// from the workspace's capacity, not from this call's n, so that calls with different n that share a
+// workspace never see another call's partial sums where they expect zeroed tickets.
+static int64_t gemv_ws_bytes_for_tiles(int64_t tiles) { return ((tiles * 4 + 255) / 256) * 256 + 8 * tiles * 128 * 4; }
+static int64_t gemv_ws_bytes(int64_t n) { return gemv_ws_bytes_for_tiles((n + 15) / 16); }
+// largest number of 16-row tiles a workspace of `bytes` can serve
+static int64_t gemv_ws_capacity(int64_t bytes) {
+  int64_t t = bytes / (4 + 8 * 128 * 4);
+  while (t > 0 && gemv_ws_bytes_for_tiles(t) > bytes) --t;
+  return t;
 }
 
 template <int D>
@@ -369,6 +375,8 @@ extern "C" int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void*
   const int chunks = static_cast<int>((k_lo + 127) / 128);
   const int hblocks = static_cast<int>(k_hi / 32);
   const bool have_ws = workspace != nullptr && workspace_bytes >= gemv_ws_bytes(n);
+  const int64_t tiles_cap = have_ws ? gemv_ws_capacity(workspace_bytes) : 0;
+  const int64_t ticket_bytes = ((tiles_cap * 4 + 255) / 256) * 256;
   int ks = 1;
   while (ks < 8 && have_ws && ((chunks + ks - 1) / ks > 32 || static_cast<int64_t>(a.tiles) * ks < 10LL * sms) &&
          chunks >= 4 * ks)
@@ -383,7 +391,7 @@ extern "C" int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void*
   const int depth = d_fit >= 8 ? 8 : (d_fit >= 4 ? 4 : 2);
   const size_t smem = x_bytes + static_cast<size_t>(depth) * kGemvWarps * kRingStageBytes + kGemvRedBytes;
   a.tickets = static_cast<unsigned int*>(workspace);
-  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ((static_cast<int64_t>(a.tiles) * 4 + 255) / 256) * 256);
+  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ticket_bytes);
   const int64_t units = static_cast<int64_t>(a.tiles) * ks;
   const int grid = static_cast<int>(units < sms ? units : sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
