@@ -147,6 +147,25 @@ PLQ_API int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void* a_
              int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
              void* y_bf16, int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
+/*
+ * plq_gemv for callers that cannot supply a workspace (no counterpart in the reference).
+ * Meant for hosts that are unable to allocate device memory on the library's behalf: a serving
+ * process that has already claimed all of HBM for its own pool, or a plugin interface that passes
+ * inputs and outputs and nothing else.  Inputs, outputs and results are exactly those of plq_gemv;
+ * the K-slice scratch is an ~8.4 MB array built into the library image (resident on every GPU
+ * that loads the library, until the process exits), which limits this entry point to
+ * n <= 32768 output features: larger n returns PLQ_ERR_LIMIT.  The call allocates and frees
+ * nothing.  The first call on each device looks up the array's device address and zeroes its
+ * ticket area; make that first call before any stream capture.  All calls on a device share the
+ * one array (it keeps the previous call's partial sums, which the next call overwrites before
+ * reading): calls that overlap on the GPU, e.g. on two streams, race and must be serialised by
+ * the caller.
+ */
+PLQ_API int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes,
+                                    const void* a_hi_sf, const void* b_lo_codes, const void* b_lo_sf,
+                                    const void* b_hi_codes, const void* b_hi_sf, int64_t m, int64_t n,
+                                    int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -399,3 +399,42 @@ extern "C" int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void*
   if (depth == 4) return launch_gemv<4>(a, grid, smem, s);
   return launch_gemv<2>(a, grid, smem, s);
 }
+
+// ---- decode GEMV for callers that cannot provide scratch memory ---------------------------------
+//
+// Some hosts of this library have no way to hand it a workspace: an inference server that reserved
+// all of HBM for its own pool at start-up (a later cudaMalloc simply fails), or a plugin that sits
+// behind an interface which passes inputs and outputs only and has no handle to the host's
+// allocator.  For them the K-slice scratch of the GEMV lives in the library image itself: a
+// file-scope device array, present on every GPU that loads the library until the process exits.
+namespace plq {
+constexpr int64_t kGemvStaticMaxRows = 32768;                         // largest n the built-in scratch serves
+constexpr int64_t kGemvStaticBytes = ((kGemvStaticMaxRows / 16 * 4 + 255) / 256) * 256 + 8 * (kGemvStaticMaxRows / 16) * 128 * 4;
+static __device__ __align__(256) unsigned char g_gemv_scratch[kGemvStaticBytes];   // ~8.4 MB; zero at load
+
+// In host code `g_gemv_scratch` is only a handle for the runtime, not an address a kernel can use:
+// the device address is looked up once per device, with that device current.
+static void* g_gemv_scratch_ptr[64];
+}  // namespace plq
+
+extern "C" int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes,
+                                       const void* a_hi_sf, const void* b_lo_codes, const void* b_lo_sf,
+                                       const void* b_hi_codes, const void* b_hi_sf, int64_t m, int64_t n,
+                                       int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy, void* stream) {
+  using namespace plq;
+  if (n > kGemvStaticMaxRows) return PLQ_ERR_LIMIT;    // built-in scratch covers n <= 32768 only
+  int dev = 0;
+  PLQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PLQ_ERR_LIMIT;
+  if (g_gemv_scratch_ptr[dev] == nullptr) {
+    // first call on this device: resolve the array's device address and make sure the tickets start at
+    // zero (they do at load; the kernel leaves them zero after every call)
+    void* ptr = nullptr;
+    PLQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_gemv_scratch));
+    PLQ_CUDA_TRY(cudaMemsetAsync(ptr, 0, ((gemv_ws_capacity(kGemvStaticBytes) * 4 + 255) / 256) * 256,
+                                 static_cast<cudaStream_t>(stream)));
+    g_gemv_scratch_ptr[dev] = ptr;
+  }
+  return plq_gemv(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf, m, n, k_lo, k_hi,
+                  y_bf16, ldy, g_gemv_scratch_ptr[dev], kGemvStaticBytes, stream);
+}
