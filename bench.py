@@ -279,6 +279,10 @@ def main_ours(args, rank, local_rank, world):
     if rank == 0:
         extra = side_benchmarks(plq, torch, dev, peaks)
 
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     gemm_tflops = fl / (gemm_ms * 1e-3) / 1e12
@@ -312,6 +316,75 @@ def main_ours(args, rank, local_rank, world):
         except Exception as exc:  # the checker library could not be built on this host
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
     print(json.dumps(line), flush=True)
+
+
+def main_model(args, rank, local_rank, world):
+    """configs[4]: random-init Llama-3-70B-architecture decoder stack, tensor-parallel over the ranks
+    (column-parallel QKV / gate_up, row-parallel O / down, one NCCL all-reduce after each row-parallel
+    linear), batch 16, prefill of 2048 random token ids + 128 greedy decode steps.  Strong scaling:
+    the job is fixed, the ranks share it."""
+    import torch
+    import torch.distributed as dist
+    import plaquant_b200 as plq
+    from plaquant_b200 import tp
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = tp.TPContext(rank, world, None)
+    cfg = LlamaConfig.llama3_70b()
+    layers = args.layers or cfg.num_layers
+    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers)
+    batch, prefill, decode = args.batch, args.prefill, args.decode
+    ids = torch.randint(0, cfg.vocab_size, (batch, prefill), generator=torch.Generator().manual_seed(40)).to(dev)
+
+    def run():
+        return model.generate(ids, decode)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+    for _ in range(max(1, min(args.warmup, 2))):
+        out = run()
+    plq.check_device_status()
+    sampler = ClockSampler(local_rank)
+    sync()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(1, min(args.steps, 5))
+    e0.record()
+    for _ in range(steps):
+        out = run()
+    e1.record()
+    sync()
+    clocks = sampler.stop()
+    plq.check_device_status()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(g, gathered[0]) for g in gathered)
+    else:
+        same = True
+    if rank == 0:
+        tokens = batch * (prefill + decode)
+        print(json.dumps({
+            "metric": "decoder tokens/s (prefill + greedy decode)", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)",
+            "data": "synthetic", "clocks": clocks, "ranks_agree_on_tokens": same,
+            "config": {"workload": f"Llama-3-70B architecture, {layers} of 80 layers, random init, batch {batch}, "
+                                   f"prefill {prefill} + {decode} greedy decode steps", "parallelism": f"tp{world}"}}),
+            flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def time_cuda(torch, fn, iters, flush=None):
@@ -471,6 +544,12 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="linears", choices=["linears", "model"],
+                    help="linears: the per-op step (default); model: the tensor-parallel decoder stack")
+    ap.add_argument("--layers", type=int, default=None, help="model workload: number of decoder layers (default 80)")
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--prefill", type=int, default=2048)
+    ap.add_argument("--decode", type=int, default=128)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -480,6 +559,8 @@ def main():
             args.m = 8 if args.case == "gemv" else M_TOKENS
         return main_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "model" and args.impl == "ours":
+        return main_model(args, rank, local_rank, world)
     if args.impl == "reference":
         main_reference(args, rank)
     else:

@@ -132,7 +132,7 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
       : "memory");
 }
 
-// 2-D tiled TMA load (no multicast): coordinates (x = innermost, y).
+// 2-D tiled TMA load into this CTA only: coordinates (x = innermost, y).
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int32_t x, int32_t y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
@@ -144,7 +144,7 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, in
 // Tiled TMA loads for kernels that may run as a CTA pair.  CG = 2 uses the pair form of the
 // instruction, whose completion bytes may be counted on an mbarrier of the other CTA of the
 // pair: `bar_addr` is a shared::cluster address (clear bit 24 of a local address to name the
-// even-ranked CTA's copy of the barrier).  No multicast: each CTA loads only its own tile.
+// even-ranked CTA's copy of the barrier).  Every CTA loads only its own tile.
 template <int CG>
 __device__ __forceinline__ void tma_load_2d_cg(uint32_t dst, const void* tmap, int32_t x, int32_t y, uint32_t bar_addr) {
   if constexpr (CG == 1)

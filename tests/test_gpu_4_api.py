@@ -96,3 +96,16 @@ def test_hadamard_matrix_and_decoder_forward():
     step = model.forward(gen[:, :1], pos0=40)
     assert rel_l2(step.cpu().numpy(), full.cpu().numpy()) < 0.05
     plq.check_device_status()
+
+
+def test_device_reported_timeout_surfaces_as_an_error():
+    """Failure detection without faulting a GPU: a kernel whose bounded wait runs out writes
+    PLQ_DEV_TIMEOUT into the status word; here the word is set from the host and the front end
+    must raise, name the cause and clear the word."""
+    from plaquant_b200 import ops
+    w = ops.status_word("cuda")
+    w.fill_(1)
+    with pytest.raises(plq.PlqError) as e:
+        plq.check_device_status()
+    assert e.value.status == 1 and "bounded wait" in str(e.value)
+    plq.check_device_status()          # cleared
