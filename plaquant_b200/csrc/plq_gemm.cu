@@ -86,6 +86,7 @@ struct GemmArgs {
   int tiles_m, tiles_n;            // tiles_m counts 128 * CG row tiles
   int lo_stages, hi_stages;        // K stages per tile in each phase
   int lo_chunks, hi_chunks;        // scale chunks per 128-row group
+  int wide_store;                  // y and ldy allow 32-byte stores
 };
 
 // Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
@@ -307,19 +308,29 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
       if (lane == 0) mbar_arrive_cluster(empty_addr + 8u * as);   // drained: the next tile may start
       if (++as == C::kAccStages) { as = 0; aphase ^= 1; }
       if (row < g.m) {
+        // Streaming stores (the output is written once and not read by this kernel: keep L2 for the
+        // operands), 32 bytes = one full sector per thread and instruction when the row allows it.
         __nv_bfloat16* yrow = g.y + static_cast<size_t>(row) * g.ldy;
+        const bool wide = g.wide_store;
 #pragma unroll
-        for (int v = 0; v < C::kColsPerEpiWarp / 8; ++v) {
-          const int col = col0 + v * 8;
-          uint32_t d[4];
+        for (int v = 0; v < C::kColsPerEpiWarp / 16; ++v) {
+          const int col = col0 + v * 16;
+          uint32_t d[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int cc = v * 8 + 2 * i;
+          for (int i = 0; i < 8; ++i) {
+            const int cc = v * 16 + 2 * i;
             asm("cvt.rn.bf16x2.f32 %0, %1, %2;"
                 : "=r"(d[i])
                 : "f"(__uint_as_float(r[cc >> 5][(cc & 31) + 1])), "f"(__uint_as_float(r[cc >> 5][cc & 31])));
           }
-          if (col < g.n) *reinterpret_cast<uint4*>(yrow + col) = make_uint4(d[0], d[1], d[2], d[3]);
+          if (wide && col + 16 <= g.n) {
+            asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow + col), "r"(d[0]),
+                         "r"(d[1]), "r"(d[2]), "r"(d[3]), "r"(d[4]), "r"(d[5]), "r"(d[6]), "r"(d[7])
+                         : "memory");
+          } else {
+            if (col < g.n) __stcs(reinterpret_cast<uint4*>(yrow + col), make_uint4(d[0], d[1], d[2], d[3]));
+            if (col + 8 < g.n) __stcs(reinterpret_cast<uint4*>(yrow + col + 8), make_uint4(d[4], d[5], d[6], d[7]));
+          }
         }
       }
     }
@@ -474,6 +485,7 @@ extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_s
   g.hi_chunks = static_cast<int>((k_hi + 127) / 128);
   g.lo_stages = (g.lo_chunks + 3) / 4;
   g.hi_stages = g.hi_chunks;
+  g.wide_store = (reinterpret_cast<uintptr_t>(y_bf16) % 32 == 0 && ldy % 16 == 0) ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (variant == PLQ_GEMM_AUTO) {
     // A CTA pair needs 30 % fewer bytes from L2 per MMA, which is what bounds large problems;
