@@ -255,17 +255,21 @@ def untile_sf(tiled: np.ndarray, rows: int, n: int) -> np.ndarray:
 # ----------------------------------------------------------------------------------------
 def _sumsq_det(x: np.ndarray) -> np.ndarray:
     """Row sum of squares, float32, in this order: inside each 128-block, four interleaved
-    partial sums p[q] (q = 0..3) run sequentially over elements 32*j + 8*q + i (j outer 0..3,
-    i inner 0..7); block sum = (p0 + p1) + (p2 + p3); blocks are combined eight at a time by
+    partial sums p[q] (q = 0..3) over elements 32*j + 8*q + i, each the sum of two chains, one
+    over the even i and one over the odd i, both run sequentially (j outer 0..3, i inner), added
+    at the end; block sum = (p0 + p1) + (p2 + p3); blocks are combined eight at a time by
     a balanced pairwise tree (missing blocks count as +0); the groups of eight are then added
     left to right."""
     rows, k = x.shape
     assert k % HAD_BLOCK == 0
     sq = (x * x).astype(F32).reshape(rows, k // 128, 4, 4, 8)   # [.., blk, j, q, i]
-    p = np.zeros((rows, k // 128, 4), dtype=F32)
+    pe = np.zeros((rows, k // 128, 4), dtype=F32)
+    po = np.zeros((rows, k // 128, 4), dtype=F32)
     for j in range(4):
-        for i in range(8):
-            p = p + sq[:, :, j, :, i]
+        for i in range(0, 8, 2):
+            pe = pe + sq[:, :, j, :, i]
+            po = po + sq[:, :, j, :, i + 1]
+    p = pe + po
     b = (p[..., 0] + p[..., 1]) + (p[..., 2] + p[..., 3])
     nb = b.shape[1]
     pad = -(-nb // 8) * 8

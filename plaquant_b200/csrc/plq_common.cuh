@@ -284,40 +284,31 @@ __device__ __forceinline__ void tc_commit(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                  : "memory");
 }
+// The tcgen05 wrappers below take 64-bit shared-memory descriptors as two 32-bit words: only the low
+// word (address field) changes between stages and K steps, so the issuing thread advances descriptors
+// with 32-bit adds and the constant high word never moves.
+#define PLQ_TC_MMA_ASM(CGSTR, KINDSTR)                                                                         \
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"                          \
+               "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"                                          \
+               "tcgen05.mma.cta_group::" CGSTR ".kind::" KINDSTR " [%0], da, db, %4, [%5], [%7], p;\n\t}" ::"r"( \
+                   d_tmem),                                                                                    \
+               "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(accumulate), "r"(sfb_tmem)   \
+               : "memory")
 template <int CG>
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  if constexpr (CG == 1)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
-            d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
-            d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  if constexpr (CG == 1) PLQ_TC_MMA_ASM("1", "mxf4nvf4.block_scale.block16");
+  else PLQ_TC_MMA_ASM("2", "mxf4nvf4.block_scale.block16");
 }
 template <int CG>
-__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  if constexpr (CG == 1)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  if constexpr (CG == 1) PLQ_TC_MMA_ASM("1", "mxf8f6f4.block_scale");
+  else PLQ_TC_MMA_ASM("2", "mxf8f6f4.block_scale");
 }
+#undef PLQ_TC_MMA_ASM
 // 32 lanes x 16 consecutive 32-bit columns from registers (thread i writes lane base + i)
 __device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -330,11 +321,17 @@ __device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t 
 // Shared -> tensor memory copy of 32 rows x 128 bit, replicated to the four lane quadrants
 // (for a CTA pair: in both CTAs, each from its own shared memory at the same offset).
 template <int CG>
-__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
   if constexpr (CG == 1)
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+    asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}" ::"r"(
+                     taddr),
+                 "r"(desc_lo), "r"(desc_hi)
+                 : "memory");
   else
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+    asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}" ::"r"(
+                     taddr),
+                 "r"(desc_lo), "r"(desc_hi)
+                 : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).

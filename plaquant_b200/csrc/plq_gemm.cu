@@ -89,25 +89,17 @@ struct GemmArgs {
   int wide_store;                  // y and ldy allow 32-byte stores
 };
 
-// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
-// groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);          // start address
-  d |= static_cast<uint64_t>(1) << 16;                          // leading byte offset (unused for swizzled K-major)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                  // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                          // descriptor version (Blackwell)
-  d |= static_cast<uint64_t>(2) << 61;                          // SWIZZLE_128B
-  return d;
-}
-// Descriptor of one 512-byte scale chunk: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  return d;
-}
+// Shared-memory matrix descriptors, split into a low word (address field, changes per stage) and a
+// constant high word.
+//   K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart:
+//     low  = start address >> 4 | leading byte offset 1 (unused for swizzled K-major) at bit 16
+//     high = stride byte offset 1024 >> 4 | descriptor version 1 at bit 46 | SWIZZLE_128B (2) at bit 61
+//   one 512-byte scale chunk, 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart:
+//     low  = start address >> 4;   high = stride byte offset 128 >> 4 | version 1 at bit 46
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr & 0x3FFFFu) >> 4; }
 // Instruction descriptor of a block-scaled MMA (K-major operands).
 //   [4,6) B scale id  [7,10) A format  [10,13) B format  [17,23) N/8  [23] scale format
 //   [24,29) M/16  [29,31) A scale id
@@ -224,10 +216,12 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         tc_commit<CG>(smem_u32(bar));
         if constexpr (CG == 2) tc_commit<CG>(smem_u32(bar) + peer_off);
       };
-      const uint64_t adesc0 = make_sw128_desc(smem_base), bdesc0 = make_sw128_desc(smem_base + kABytes);
-      const uint64_t sfdesc0 = make_sf_desc(smem_base + kABytes + C::kBBytes);
+      // Descriptors as (low word, constant high word); the low word of stage s is base + s * stage bytes / 16.
+      const uint32_t a_lo0 = desc_lo_sw128(smem_base), b_lo0 = desc_lo_sw128(smem_base + kABytes);
+      const uint32_t sf_lo0 = desc_lo_sf(smem_base + kABytes + C::kBBytes);
+      constexpr uint32_t kStageStep = C::kStageBytes >> 4, kChunkStep = kSfChunk >> 4, kSfbOff = C::kSfaBytes >> 4;
       int s = 0, as = 0;
-      uint32_t phase = 0, aphase = 0, set = 0;
+      uint32_t phase = 0, aphase = 0, set = 0, soff = 0;
       bool ok = true;
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         ok = CG == 2 ? mbar_wait_bounded_cluster(&acc_empty[as], aphase ^ 1, abort_flag)
@@ -245,36 +239,58 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
           const int kk = lo ? ks : ks - g.lo_stages;
           const uint32_t sfa_t = tmem_base + C::kSfCol0 + set * C::kSfSetCols, sfb_t = sfa_t + 16;
           set ^= 1u;
-          const uint32_t soff = static_cast<uint32_t>(s) * (C::kStageBytes >> 4);   // in 16-byte units
-          const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff, sfa_d = sfdesc0 + soff;
-          const uint64_t sfb_d = sfa_d + (C::kSfaBytes >> 4);
+          const uint32_t a_lo = a_lo0 + soff, b_lo = b_lo0 + soff, sf_lo = sf_lo0 + soff;
           const int nmma = lo ? min(4, g.lo_chunks - kk * 4) : min(4, (g.k_hi - kk * 128) / 32);
-          // scale chunks shared -> tensor memory, ahead of the MMAs that read them
-          const int nchunk = lo ? nmma : 1;
-          for (int h = 0; h < nchunk; ++h) {
-            tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, sfa_d + h * (kSfChunk >> 4));
+          // Scale chunks go shared -> tensor memory ahead of the MMAs that read them (the copies run
+          // beside earlier MMAs in the tensor pipe).  The full stage is straight-line code with
+          // immediate offsets: the issue rate of this one thread is what bounds the kernel otherwise.
+          if (lo && nmma == 4) {
 #pragma unroll
-            for (int q = 0; q < C::kSfGroups; ++q)
-              tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, sfb_d + (q * 4 + h) * (kSfChunk >> 4));
-          }
-          if (lo) {
+            for (int h = 0; h < 4; ++h) {
+              tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, sf_lo + h * kChunkStep, kDescHiSf);
+#pragma unroll
+              for (int q = 0; q < C::kSfGroups; ++q)
+                tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, sf_lo + kSfbOff + (q * 4 + h) * kChunkStep,
+                                         kDescHiSf);
+            }
+            // advance 32 bytes (64 E2M1) inside the swizzle span: +2 in the address field
+            tc_mma_nvf4<CG>(d_tmem, a_lo, b_lo, kDescHiSw128, idesc_lo, sfa_t, sfb_t, accumulate);
+#pragma unroll
+            for (int h = 1; h < 4; ++h)
+              tc_mma_nvf4<CG>(d_tmem, a_lo + 2 * h, b_lo + 2 * h, kDescHiSw128, idesc_lo, sfa_t + 4 * h,
+                              sfb_t + (BN / 32) * h, 1u);
+          } else if (lo) {
             for (int h = 0; h < nmma; ++h) {
-              // advance 32 bytes (64 E2M1) inside the swizzle span: +2 in the address field
-              tc_mma_nvf4<CG>(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc_lo, sfa_t + 4 * h, sfb_t + (BN / 32) * h,
-                              accumulate);
+              tc_cp_32x128b_warpx4<CG>(sfa_t + 4 * h, sf_lo + h * kChunkStep, kDescHiSf);
+#pragma unroll
+              for (int q = 0; q < C::kSfGroups; ++q)
+                tc_cp_32x128b_warpx4<CG>(sfb_t + (BN / 32) * h + 4 * q, sf_lo + kSfbOff + (q * 4 + h) * kChunkStep,
+                                         kDescHiSf);
+            }
+            for (int h = 0; h < nmma; ++h) {
+              tc_mma_nvf4<CG>(d_tmem, a_lo + 2 * h, b_lo + 2 * h, kDescHiSw128, idesc_lo, sfa_t + 4 * h,
+                              sfb_t + (BN / 32) * h, accumulate);
               accumulate = 1;
             }
           } else {
+            // MXFP8: one chunk per stage; scale id h selects byte h of every scale column (mirrored in
+            // the top bits of the tensor-memory address)
+            tc_cp_32x128b_warpx4<CG>(sfa_t, sf_lo, kDescHiSf);
+#pragma unroll
+            for (int q = 0; q < C::kSfGroups; ++q)
+              tc_cp_32x128b_warpx4<CG>(sfb_t + 4 * q, sf_lo + kSfbOff + q * 4 * kChunkStep, kDescHiSf);
             for (int h = 0; h < nmma; ++h) {
-              // scale id h selects byte h of every scale column; mirrored in the address' top bits
               const uint32_t idesc = idesc_hi | (static_cast<uint32_t>(h) << 4) | (static_cast<uint32_t>(h) << 29);
-              tc_mma_mxf8<CG>(d_tmem, adesc + 2 * h, bdesc + 2 * h, idesc, sfa_t + (static_cast<uint32_t>(h) << 30),
-                              sfb_t + (static_cast<uint32_t>(h) << 30), accumulate);
+              tc_mma_mxf8<CG>(d_tmem, a_lo + 2 * h, b_lo + 2 * h, kDescHiSw128, idesc,
+                              sfa_t + (static_cast<uint32_t>(h) << 30), sfb_t + (static_cast<uint32_t>(h) << 30),
+                              accumulate);
               accumulate = 1;
             }
           }
+          accumulate = 1;
           commit_all(&empty_bar[s]);                 // stage reusable once these MMAs have read it
-          if (++s == C::kStages) { s = 0; phase ^= 1; }
+          soff += kStageStep;
+          if (++s == C::kStages) { s = 0; soff = 0; phase ^= 1; }
         }
         if (!ok) break;
         commit_all(&acc_full[as]);                   // accumulator complete (in both CTAs of a pair)

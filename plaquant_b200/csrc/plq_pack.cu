@@ -37,7 +37,9 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   const int q = tid & 3;
   const int k0 = (tid >> 2) * 128;                  // first element of this quad's block
   const int lane = tid & 31;
-  float v[32];
+  // v2[p] holds elements (2p, 2p+1) of the lane's 32, i.e. e = 8*j + i -> p = 4*j + i/2.  Arithmetic on
+  // pairs uses the packed float32x2 instructions of sm_100 (same IEEE rounding per element, half the issue slots).
+  float2 v2[16];
 
   // ---- load: four 16-byte pieces per lane ---------------------------------------------
   const uint4* xrow = a.x + static_cast<size_t>(row) * (a.k >> 3);
@@ -46,18 +48,19 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
     const int kk = k0 + 32 * j + 8 * q;
     uint4 w = make_uint4(0, 0, 0, 0);
     if (kk < a.k) w = __ldg(xrow + (kk >> 3));
-    v[8 * j + 0] = bf16lo_to_f32(w.x); v[8 * j + 1] = bf16hi_to_f32(w.x);
-    v[8 * j + 2] = bf16lo_to_f32(w.y); v[8 * j + 3] = bf16hi_to_f32(w.y);
-    v[8 * j + 4] = bf16lo_to_f32(w.z); v[8 * j + 5] = bf16hi_to_f32(w.z);
-    v[8 * j + 6] = bf16lo_to_f32(w.w); v[8 * j + 7] = bf16hi_to_f32(w.w);
+    v2[4 * j + 0] = make_float2(bf16lo_to_f32(w.x), bf16hi_to_f32(w.x));
+    v2[4 * j + 1] = make_float2(bf16lo_to_f32(w.y), bf16hi_to_f32(w.y));
+    v2[4 * j + 2] = make_float2(bf16lo_to_f32(w.z), bf16hi_to_f32(w.z));
+    v2[4 * j + 3] = make_float2(bf16lo_to_f32(w.w), bf16hi_to_f32(w.w));
   }
 
   // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
   if constexpr (NORM) {
     __shared__ float warp_sums[32];
-    float s = 0.0f;
+    float2 s2 = make_float2(0.0f, 0.0f);               // even and odd elements accumulate separately
 #pragma unroll
-    for (int e = 0; e < 32; ++e) s = fmaf(v[e], v[e], s);     // v*v is exact for bf16 inputs
+    for (int p = 0; p < 16; ++p) s2 = __ffma2_rn(v2[p], v2[p], s2);   // v*v is exact for bf16 inputs
+    float s = __fadd_rn(s2.x, s2.y);
     s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 1);
     s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 2);              // (p0+p1)+(p2+p3): block sum
     s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 4);
@@ -70,6 +73,7 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
     for (int w = 0; w < nwarps; ++w) tot = tot + warp_sums[w];  // left to right
     const float var = __fdiv_rn(tot, static_cast<float>(a.k));
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+    const float2 r2 = make_float2(r, r);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int kk = k0 + 32 * j + 8 * q;
@@ -78,54 +82,61 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
       const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
-        const float y0 = __fmul_rn(bf16lo_to_f32(gw[p]), __fmul_rn(v[8 * j + 2 * p], r));
-        const float y1 = __fmul_rn(bf16hi_to_f32(gw[p]), __fmul_rn(v[8 * j + 2 * p + 1], r));
-        const uint32_t b = f32x2_to_bf16x2(y0, y1);
-        v[8 * j + 2 * p] = bf16lo_to_f32(b);
-        v[8 * j + 2 * p + 1] = bf16hi_to_f32(b);
+        const float2 y = __fmul2_rn(make_float2(bf16lo_to_f32(gw[p]), bf16hi_to_f32(gw[p])), __fmul2_rn(v2[4 * j + p], r2));
+        const uint32_t b = f32x2_to_bf16x2(y.x, y.y);
+        v2[4 * j + p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
       }
     }
   }
 
   // ---- block-Hadamard(128): strides 1,2,4 | 8,16 (shuffles) | 32,64, then * 1/sqrt(128) ----
   if constexpr (HAD) {
+    const float2 neg1 = make_float2(-1.0f, -1.0f);
 #pragma unroll
-    for (int h = 1; h < 8; h <<= 1) {
+    for (int p = 0; p < 16; ++p) {                       // stride 1: inside a pair
+      const float x0 = v2[p].x, x1 = v2[p].y;
+      v2[p] = make_float2(__fadd_rn(x0, x1), __fsub_rn(x0, x1));
+    }
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        if ((e & h) == 0) {
-          const float x0 = v[e], x1 = v[e + h];
-          v[e] = __fadd_rn(x0, x1);
-          v[e + h] = __fsub_rn(x0, x1);
+    for (int h = 1; h < 4; h <<= 1) {                    // strides 2, 4: pairs p, p + h
+#pragma unroll
+      for (int p = 0; p < 16; ++p) {
+        if ((p & h) == 0) {
+          const float2 x0 = v2[p], x1 = v2[p + h];
+          v2[p] = __fadd2_rn(x0, x1);
+          v2[p + h] = __ffma2_rn(x1, neg1, x0);          // x0 - x1: exact product, one rounding
         }
       }
     }
 #pragma unroll
-    for (int m = 1; m <= 2; m <<= 1) {
-      const float sgn = (q & m) ? -1.0f : 1.0f;      // upper lane of the pair computes partner - own
+    for (int m = 1; m <= 2; m <<= 1) {                   // strides 8, 16: across the quad
+      const float sg = (q & m) ? -1.0f : 1.0f;           // upper lane of the pair computes partner - own
+      const float2 sgn = make_float2(sg, sg);
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const float o = __shfl_xor_sync(0xFFFFFFFFu, v[e], m);
-        v[e] = fmaf(sgn, v[e], o);                   // exact product, one rounding: own+other / other-own
+      for (int p = 0; p < 16; ++p) {
+        float2 o;
+        o.x = __shfl_xor_sync(0xFFFFFFFFu, v2[p].x, m);
+        o.y = __shfl_xor_sync(0xFFFFFFFFu, v2[p].y, m);
+        v2[p] = __ffma2_rn(sgn, v2[p], o);               // own + other / other - own
       }
     }
 #pragma unroll
-    for (int h = 8; h < 32; h <<= 1) {
+    for (int h = 4; h < 16; h <<= 1) {                   // strides 32, 64: pairs p, p + h
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        if ((e & h) == 0) {
-          const float x0 = v[e], x1 = v[e + h];
-          v[e] = __fadd_rn(x0, x1);
-          v[e + h] = __fsub_rn(x0, x1);
+      for (int p = 0; p < 16; ++p) {
+        if ((p & h) == 0) {
+          const float2 x0 = v2[p], x1 = v2[p + h];
+          v2[p] = __fadd2_rn(x0, x1);
+          v2[p + h] = __ffma2_rn(x1, neg1, x0);
         }
       }
     }
+    const float2 scale = make_float2(0.088388347648318441f, 0.088388347648318441f);
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      const uint32_t b = f32x2_to_bf16x2(__fmul_rn(v[e], 0.088388347648318441f),
-                                         __fmul_rn(v[e + 1], 0.088388347648318441f));
-      v[e] = bf16lo_to_f32(b);
-      v[e + 1] = bf16hi_to_f32(b);
+    for (int p = 0; p < 16; ++p) {
+      const float2 y = __fmul2_rn(v2[p], scale);
+      const uint32_t b = f32x2_to_bf16x2(y.x, y.y);
+      v2[p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
     }
   }
 
@@ -137,9 +148,10 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
     float x8[8];
     float m = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      x8[i] = v[8 * j + i];
-      m = fmaxf(m, fabsf(x8[i]));
+    for (int i = 0; i < 4; ++i) {
+      x8[2 * i] = v2[4 * j + i].x;
+      x8[2 * i + 1] = v2[4 * j + i].y;
+      m = fmaxf(m, fmaxf(fabsf(x8[2 * i]), fabsf(x8[2 * i + 1])));
     }
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     const float m32 = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));

@@ -58,11 +58,15 @@ __device__ __forceinline__ uint32_t nvfp4_scale_code(float bmax) {
 // Eight float32 (bf16-valued) -> eight E2M1 codes, element 0 in bits [0,4).
 __device__ __forceinline__ uint32_t nvfp4_quantize8(const float (&x)[8], float s, float r) {
   float q[8];
+  const float2 r2 = make_float2(r, r), ns2 = make_float2(-s, -s);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float q0 = x[i] * r;
-    const float e = fmaf(-s, q0, x[i]);
-    q[i] = fmaf(e, r, q0);
+  for (int i = 0; i < 8; i += 2) {
+    const float2 xv = make_float2(x[i], x[i + 1]);
+    const float2 q0 = __fmul2_rn(xv, r2);
+    const float2 e = __ffma2_rn(ns2, q0, xv);
+    const float2 q1 = __ffma2_rn(e, r2, q0);
+    q[i] = q1.x;
+    q[i + 1] = q1.y;
   }
   uint32_t out;
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
@@ -73,11 +77,10 @@ __device__ __forceinline__ uint32_t nvfp4_quantize8(const float (&x)[8], float s
       "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
       : "=r"(out)
       : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
-  // clear the sign nibble-bit of elements whose quotient is exactly zero (x == +-0)
-  uint32_t keep = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) keep |= (q[i] != 0.0f ? 0xFu : 0x7u) << (4 * i);
-  return out & keep;
+  // No sign fix-up is needed here: the quotient is zero only for x = +-0, and for x = -0 the two
+  // refinement FMAs already turn it into +0 (e = (-s)(-0) + (-0) = +0, q = (+0) r + (-0) = +0), which is
+  // what the reference's sign(x/s) * |q| gives; a negative x that merely rounds to zero keeps its sign.
+  return out;
 }
 
 // MXFP8 block scale byte (exponent + 127) from the block's absolute maximum (bf16-valued).
