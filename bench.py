@@ -461,14 +461,14 @@ def side_benchmarks(plq, torch, dev, peaks):
     gv = {}
     for name, k, n, _ in SHAPES:
         w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
-        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="tiled")
         del w
         pws = clone_packed(plq, pw, max(2, int(400e6 // pw.nbytes())))      # >= 400 MB of weights in rotation
         for m in (1, 2, 4, 8):
             xa = plq.pack(x[:m, :k] if k <= 4096 else torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev),
-                          k // 32, hadamard=True, sf_layout="rowmajor")
+                          k // 32, hadamard=True, sf_layout="tiled")
             y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-            fns = [(lambda w=w_: plq.gemv(xa, w, out=y)) for w_ in pws]
+            fns = [(lambda w=w_: plq.gemv_tc(xa, w, out=y)) for w_ in pws]
             ms = time_rotating(torch, fns, 5)
             nb = pw.nbytes() + xa.nbytes() + m * n * 2
             gv[f"{name}_m{m}"] = {"us": ms * 1e3, "bytes": nb, "gbs": nb / (ms * 1e-3) / 1e9,
@@ -500,14 +500,15 @@ def main_case(args):
         pa = plq.alloc_packed(4096, 4096, 128, "tiled", dev)
         fn = lambda: plq.pack(x, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pa)
         work, unit = 2 * 4096 * 4096 + 2 * 4096 + 4096 * 2364, "GB/s"
-    elif args.case == "gemv":
+    elif args.case in ("gemv", "gemv_tc"):
+        layout, op = ("rowmajor", plq.gemv) if args.case == "gemv" else ("tiled", plq.gemv_tc)
         w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
-        pw = plq.pack(w, k // 32, hadamard=True, sf_layout="rowmajor")
-        pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout="rowmajor")
+        pw = plq.pack(w, k // 32, hadamard=True, sf_layout=layout)
+        pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout=layout)
         y = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
         pws = clone_packed(plq, pw, max(2, int(400e6 // pw.nbytes())))
-        rot = [(lambda w=w_: plq.gemv(pa, w, out=y)) for w_ in pws]
-        fn = lambda: plq.gemv(pa, pw, out=y)
+        rot = [(lambda w=w_: op(pa, w, out=y)) for w_ in pws]
+        fn = lambda: op(pa, pw, out=y)
         work, unit = pw.nbytes() + pa.nbytes() + y.numel() * 2, "GB/s"
     else:
         w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
@@ -521,13 +522,13 @@ def main_case(args):
         fn()
     torch.cuda.synchronize()
     ms = time_cuda(torch, fn, args.steps, flush)
-    if args.case == "gemv":
+    if args.case in ("gemv", "gemv_tc"):
         ms_rot = time_rotating(torch, rot, max(1, args.steps // 4))
     plq.check_device_status()
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
     line = {"case": args.case, "shape": name, "m": args.m, "us_per_launch": ms * 1e3, "rate": rate, "unit": unit,
             "work": work}
-    if args.case == "gemv":
+    if args.case in ("gemv", "gemv_tc"):
         line["us_back_to_back"] = ms_rot * 1e3
         line["rate_back_to_back"] = work / (ms_rot * 1e-3) / 1e9
     print(json.dumps(line), flush=True)
@@ -535,7 +536,7 @@ def main_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["pack", "gemv", "gemm"],
+    ap.add_argument("--case", default=None, choices=["pack", "gemv", "gemv_tc", "gemm"],
                     help="run one kernel on one fixed case instead of the full step")
     ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
     ap.add_argument("--m", type=int, default=None)
@@ -556,7 +557,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.case is not None:
         if args.m is None:
-            args.m = 8 if args.case == "gemv" else M_TOKENS
+            args.m = 8 if args.case in ("gemv", "gemv_tc") else M_TOKENS
         return main_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "model" and args.impl == "ours":

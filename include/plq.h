@@ -166,6 +166,25 @@ PLQ_API int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf,
                                     const void* b_hi_codes, const void* b_hi_sf, int64_t m, int64_t n,
                                     int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy, void* stream);
 
+/*
+ * Decode GEMV on the tensor cores, m <= 8: same operands and scale layout as plq_mixed_gemm
+ * (A = packed activations, B = packed weights, both with PLQ_SF_TILED scale buffers), same result
+ * contract.  The weight rows are the 128-row side of the block-scaled tcgen05.mma and the m
+ * activation rows the narrow side, so the packed weights stream HBM -> shared memory -> tensor core
+ * untouched by any thread.  When n gives fewer 128-row tiles than SMs, a thread-block cluster of up
+ * to 8 CTAs shares each tile along K and combines the partial sums through distributed shared
+ * memory in a fixed order; no scratch memory is needed and results do not depend on timing.
+ * The kernel is launched with programmatic stream serialisation: it may start (set-up, first
+ * weight loads) while the previous kernel of the stream drains, and waits for that kernel's
+ * completion before reading the activations or writing y.  `dev_status` as for plq_mixed_gemm.
+ * Replaces the same reference lines as plq_gemv (the quantised linear at decode batch sizes,
+ * promix/quantize/quant_utils.py:389 / inference/forward_pass.py:319).
+ */
+PLQ_API int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+                        const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+                        int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
+                        void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -347,6 +347,21 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[3
       : "r"(taddr)
       : "memory");
 }
+// Programmatic dependent launch.  `pdl_launch_dependents`: the next kernel in the stream, if it was
+// launched with programmatic stream serialisation, may start once every CTA of this grid has executed
+// this (or exited).  `pdl_wait`: blocks until the preceding grid has completed and its writes are visible;
+// everything a kernel does before it must not depend on, or disturb, earlier kernels.  Both are no-ops
+// for ordinary launches.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// 32 lanes x 8 consecutive 32-bit columns
+__device__ __forceinline__ void tc_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 #endif  // __CUDACC__

@@ -32,6 +32,9 @@ struct PackArgs {
 
 template <bool NORM, bool HAD>
 __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
+  // A consumer launched with programmatic stream serialisation (the decode GEMV) may set itself up and
+  // prefetch its weights while this kernel runs; it waits for this grid's completion before reading the codes.
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const int q = tid & 3;

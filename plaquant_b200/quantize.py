@@ -112,10 +112,9 @@ class QuantizedLinear:
         return self.forward(x, **kw)
 
     def quantize_input(self, x: torch.Tensor, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6):
-        """[RMSNorm] -> [Hadamard] -> pack of x[..., K]; row-major scales for <= 8 rows (GEMV), tiled otherwise."""
-        rows = x.numel() // x.shape[-1]
-        layout = "rowmajor" if rows <= 8 else "tiled"
-        return ops.pack(x, self.high_bits_length, hadamard=self.online_had, sf_layout=layout, gamma=norm_weight,
+        """[RMSNorm] -> [Hadamard] -> pack of x[..., K] with tiled scales (what both the GEMM and the tensor-core
+        GEMV read)."""
+        return ops.pack(x, self.high_bits_length, hadamard=self.online_had, sf_layout="tiled", gamma=norm_weight,
                         eps=eps)
 
     def forward(self, x, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
@@ -130,7 +129,9 @@ class QuantizedLinear:
         else:
             pa, lead = self.quantize_input(x, norm_weight, eps), x.shape[:-1]
         if pa.sf_layout == ops.SF_ROWMAJOR:
-            y = ops.gemv(pa, self._gemv_w)
+            y = ops.gemv(pa, self._gemv_w)             # a caller-packed operand in the spec's row-major layout
+        elif pa.rows <= 8:
+            y = ops.gemv_tc(pa, self._gemm_w)          # decode: stream the weights once
         else:
             y = ops.mixed_gemm(pa, self._gemm_w)
         return y.view(*lead, self.out_features)

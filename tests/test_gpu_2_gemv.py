@@ -57,3 +57,48 @@ def test_gemv_argument_errors():
     with pytest.raises(plq.PlqError) as e:
         plq.gemv(pa, pa)          # m = 9 > 8
     assert e.value.status == -2
+
+
+# ---- tensor-core GEMV (tiled scale layout, the operands of the fused GEMM) ----------------------
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 3])
+@pytest.mark.parametrize("n,k,k_hi", [(256, 4096, 128), (200, 14336, 448), (136, 192, 64), (16, 64, 0),
+                                       (128, 128, 128), (1024, 8192, 256), (8, 13952, 64)])
+def test_gemv_tc_against_oracle(m, n, k, k_hi):
+    x = synth_activation(m, k, seed=10 * m + 1)
+    w = synth_weight(n, k, seed=n + k)
+    had = k % 128 == 0
+    pa = plq.pack(x.cuda(), k_hi, hadamard=had, sf_layout="tiled")
+    pb = plq.pack(w.cuda(), k_hi, hadamard=had, sf_layout="tiled")
+    y = f32_of(plq.gemv_tc(pa, pb))
+    plq.check_device_status()
+    want = F.round_to_bf16(F.linear(packed_to_numpy(pa), packed_to_numpy(pb)))
+    r = rel_l2(y, want)
+    assert r <= TOL, r
+
+
+@pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
+def test_llama8b_shapes_gemv_tc(n, k):
+    """Full decode shapes at m = 8: agreement with the fused GEMM on the identical operands, a sample of
+    output columns against the oracle, and run-to-run determinism."""
+    k_hi = k // 32
+    xc, wc = synth_activation(8, k, seed=42).cuda(), synth_weight(n, k, seed=n // 7 + k).cuda()
+    pa = plq.pack(xc, k_hi, hadamard=True, sf_layout="tiled")
+    pb = plq.pack(wc, k_hi, hadamard=True, sf_layout="tiled")
+    y = plq.gemv_tc(pa, pb)
+    assert torch.equal(y, plq.gemv_tc(pa, pb))
+    yg = plq.mixed_gemm(pa, pb)
+    plq.check_device_status()
+    assert rel_l2(f32_of(y), f32_of(yg)) <= TOL
+    sel = np.sort(np.random.default_rng(2).choice(n, 64, replace=False))
+    nb = packed_to_numpy(pb)
+    sub = {**nb, "rows": len(sel), **{key: nb[key][sel] for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf")}}
+    want = F.round_to_bf16(F.linear(packed_to_numpy(pa), sub))
+    assert rel_l2(f32_of(y)[:, sel], want) <= TOL
+
+
+def test_gemv_tc_argument_errors():
+    x = synth_activation(9, 256, seed=1).cuda()
+    pa = plq.pack(x, 64, sf_layout="tiled")
+    with pytest.raises(plq.PlqError) as e:
+        plq.gemv_tc(pa, pa)          # m = 9 > 8
+    assert e.value.status == -2
