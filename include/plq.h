@@ -167,10 +167,10 @@ PLQ_API int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf,
                                     int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy, void* stream);
 
 /*
- * Decode GEMV on the tensor cores, m <= 8: same operands and scale layout as plq_mixed_gemm
+ * Decode GEMV on the tensor cores, m <= 16: same operands and scale layout as plq_mixed_gemm
  * (A = packed activations, B = packed weights, both with PLQ_SF_TILED scale buffers), same result
  * contract.  The weight rows are the 128-row side of the block-scaled tcgen05.mma and the m
- * activation rows the narrow side, so the packed weights stream HBM -> shared memory -> tensor core
+ * activation rows the narrow side (N = 16 of the instruction), so the packed weights stream HBM -> shared memory -> tensor core
  * untouched by any thread.  When n gives fewer 128-row tiles than SMs, a thread-block cluster of up
  * to 8 CTAs shares each tile along K and combines the partial sums through distributed shared
  * memory in a fixed order; no scratch memory is needed and results do not depend on timing.

@@ -1,4 +1,4 @@
-// Decode GEMV on the tensor cores, m <= 8:  Y[m, n] = deq(X)[m, :] . deq(W)[n, :]  (bf16 out)
+// Decode GEMV on the tensor cores, m <= 16:  Y[m, n] = deq(X)[m, :] . deq(W)[n, :]  (bf16 out)
 //
 // The weights are the M-side operand of the block-scaled MMA (128 weight rows per instruction)
 // and the activations the N-side one (m rows, zero-filled to 16 by the TMA box), so the packed
@@ -36,7 +36,7 @@ constexpr int kGtN = 16;                                   // MMA N (activation 
 constexpr int kGtXBytes = kGtN * kStageKBytes;             // 2 KiB
 constexpr int kGtSfBytes = 4 * kSfChunk;                   // 2 KiB: four chunks of one 128-row group
 constexpr int kGtStageBytes = kABytes + kGtXBytes + 2 * kGtSfBytes;
-constexpr int kGtStages = 8;
+template <int MR> constexpr int kGtStagesFor = MR == 8 ? 8 : 7;   // the partial-sum slots take shared memory too
 constexpr uint32_t kGtProducers = 3;                         // warps 0, 2, 3: one thread each, stages round-robin
 constexpr int kGtAccStages = 2;
 constexpr int kGtAccCols = 32;                             // spacing of the two accumulators (16 used)
@@ -45,12 +45,12 @@ constexpr int kGtSfSetCols = 32;                           // 4 MMAs x (4 weight
 constexpr int kGtTmemCols = 128;
 constexpr int kGtThreads = 256;
 constexpr int kGtEpiThreads = 128;
-constexpr int kGtSlotFloats = 8 * 128;                     // one partial: 8 activation rows x 128 weight rows
 constexpr int kGtMaxSlices = 8;                            // portable cluster size
-constexpr int kGtSlotBytes = kGtSlotFloats * 4;            // 4 KiB
-constexpr size_t kGtSmemBytes = 1024 + static_cast<size_t>(kGtStages) * kGtStageBytes + (kGtMaxSlices - 1) * kGtSlotBytes + 512;
+template <int MR> constexpr int kGtSlotBytesFor = MR * 128 * 4;      // one partial: MR activation rows x 128 weight rows, float32
+template <int MR>
+constexpr size_t kGtSmemBytesFor = 1024 + static_cast<size_t>(kGtStagesFor<MR>) * kGtStageBytes + (kGtMaxSlices - 1) * kGtSlotBytesFor<MR> + 512;
 static_assert(kGtSfCol0 + 2 * kGtSfSetCols <= kGtTmemCols, "tensor memory budget");
-static_assert(kGtSmemBytes <= 232448, "shared memory budget");
+static_assert(kGtSmemBytesFor<8> <= 232448 && kGtSmemBytesFor<16> <= 232448, "shared memory budget");
 
 struct GtMaps {
   CUtensorMap w_lo, x_lo, w_hi, x_hi, sfw_lo, sfx_lo, sfw_hi, sfx_hi;
@@ -84,7 +84,12 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
+// MR = 8 or 16: how many activation rows (accumulator columns) the epilogue handles.
+template <int MR>
 __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_constant__ GtMaps maps, const GtArgs g) {
+  constexpr int kGtStages = kGtStagesFor<MR>;
+  constexpr int kGtSlotBytes = kGtSlotBytesFor<MR>;
+  constexpr int kGtSlotFloats = MR * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* slots = reinterpret_cast<float*>(smem + static_cast<size_t>(kGtStages) * kGtStageBytes);   // CTA 0: partials of CTAs 1..S-1
@@ -265,21 +270,29 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
       ok = epi_all(ok);                               // one decision for the four warps
       if (!ok) break;
       tc_fence_after();
-      uint32_t r[8];
-      tc_ld_32x32b_x8(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * kGtAccCols, r);
+      uint32_t r[MR];
+      if constexpr (MR == 8) {
+        tc_ld_32x32b_x8(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * kGtAccCols, r);
+      } else {
+        uint32_t h0[8], h1[8];
+        tc_ld_32x32b_x8(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * kGtAccCols, h0);
+        tc_ld_32x32b_x8(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * kGtAccCols + 8, h1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { r[j] = h0[j]; r[8 + j] = h1[j]; }
+      }
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
       if (++as == kGtAccStages) { as = 0; aphase ^= 1; }
-      float acc[8];
+      float acc[MR];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = __uint_as_float(r[j]);
+      for (int j = 0; j < MR; ++j) acc[j] = __uint_as_float(r[j]);
       if (slice > 0) {
         // push this slice's partial sums into CTA 0's slot (slice - 1), then arrive (release) on its barrier
         const uint32_t dst = map_to_cta(smem_u32(slots), 0u) + static_cast<uint32_t>((slice - 1) * kGtSlotBytes + trow * 4);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) st_cluster_f32(dst + j * 512, acc[j]);
+        for (int j = 0; j < MR; ++j) st_cluster_f32(dst + j * 512, acc[j]);
         mbar_arrive_cluster(map_to_cta(smem_u32(red_bar), 0u));
         continue;
       }
@@ -292,13 +305,13 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
         }
         for (int sl = 0; sl < nslice - 1; ++sl) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += slots[sl * kGtSlotFloats + j * 128 + trow];
+          for (int j = 0; j < MR; ++j) acc[j] += slots[sl * kGtSlotFloats + j * 128 + trow];
         }
       }
       const int row = (first_tile + t * tile_step) * kBM + trow;
       if (row < g.n) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < MR; ++j)
           if (j < g.m) g.y[static_cast<size_t>(j) * g.ldy + row] = __float2bfloat16_rn(acc[j]);
       }
     }
@@ -325,20 +338,21 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
 // ---- host side --------------------------------------------------------------------------------
 // How many clusters of each size the device can hold at once (one CTA per SM, clusters inside a GPC);
 // looked up once per thread and device.
+template <int MR>
 static int gt_max_clusters(int slices) {
   static thread_local int cached_dev = -1;
   static thread_local int table[kGtMaxSlices + 1];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   if (cached_dev != dev) {
-    if (cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kGtSmemBytes)) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemv_tc_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kGtSmemBytesFor<MR>)) != cudaSuccess)
       return 0;
     for (int s = 1; s <= kGtMaxSlices; ++s) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(static_cast<unsigned>(s * 64), 1, 1);
       cfg.blockDim = dim3(kGtThreads, 1, 1);
-      cfg.dynamicSmemBytes = kGtSmemBytes;
+      cfg.dynamicSmemBytes = kGtSmemBytesFor<MR>;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = static_cast<unsigned>(s);
@@ -347,7 +361,7 @@ static int gt_max_clusters(int slices) {
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, gemv_tc_kernel, &cfg) != cudaSuccess) n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemv_tc_kernel<MR>, &cfg) != cudaSuccess) n = 0;
       table[s] = n;
     }
     (void)cudaGetLastError();
@@ -358,16 +372,42 @@ static int gt_max_clusters(int slices) {
 
 // K slices per tile (= cluster size) and grid: the largest slice count for which every tile's cluster is
 // resident at once; one slice (CTAs looping over whole tiles) when there are more tiles than that.
+template <int MR>
 static void gt_plan(int64_t n, int64_t k_lo, int64_t k_hi, int sms, int* slices, int* grid) {
   const int tiles = static_cast<int>((n + kBM - 1) / kBM);
   const int k_stages = static_cast<int>((k_lo / 64 + 3) / 4 + (k_hi + 127) / 128);
   int s = sms / tiles;
   if (s > kGtMaxSlices) s = kGtMaxSlices;
   if (s > k_stages) s = k_stages;
-  while (s > 1 && gt_max_clusters(s) < tiles) --s;
+  while (s > 1 && gt_max_clusters<MR>(s) < tiles) --s;
   if (s < 1) s = 1;
   *slices = s;
   *grid = s > 1 ? tiles * s : (tiles < sms ? tiles : sms);
+}
+
+template <int MR>
+static int gt_launch(const GtMaps& tm, const GtArgs& g, int64_t n, int64_t k_lo, int64_t k_hi, cudaStream_t stream) {
+  int slices = 1, grid = 1;
+  if (gt_max_clusters<MR>(1) < 1) return PLQ_ERR_CUDA;     // also sets the kernel's shared-memory attribute
+  gt_plan<MR>(n, k_lo, k_hi, sm_count(), &slices, &grid);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kGtThreads, 1, 1);
+  cfg.dynamicSmemBytes = kGtSmemBytesFor<MR>;
+  cfg.stream = stream;
+  // Programmatic dependent launch: this kernel may start while the previous one in the stream drains; it
+  // touches nothing that depends on earlier work before its griddepcontrol.wait.
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = static_cast<unsigned>(slices);
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_tc_kernel<MR>, tm, g));
+  return PLQ_OK;
 }
 
 }  // namespace plq
@@ -377,7 +417,7 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
                            int64_t m, int64_t n, int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy,
                            int32_t* dev_status, void* stream) {
   using namespace plq;
-  if (m < 1 || m > 8 || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0 || ldy < n) return PLQ_ERR_SHAPE;
+  if (m < 1 || m > kGtN || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0 || ldy < n) return PLQ_ERR_SHAPE;
   if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
   if (n > (1 << 30) || k_lo > (1 << 24) || k_hi > (1 << 24)) return PLQ_ERR_LIMIT;
   if (!y_bf16 || !dev_status) return PLQ_ERR_NULL;
@@ -399,8 +439,6 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
   g.lo_stages = (g.lo_chunks + 3) / 4;
   g.hi_stages = static_cast<int>((k_hi + 127) / 128);
   g.tiles = static_cast<int>((n + kBM - 1) / kBM);
-  int slices = 1, grid = 1;
-  gt_plan(n, k_lo, k_hi, sm_count(), &slices, &grid);
 
   GtMaps tm;
   memset(&tm, 0, sizeof(tm));
@@ -417,23 +455,6 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
     if ((st = make_sf_tmap(&tm.sfw_hi, b_hi_sf, g.hi_stages, groups, 1)) != PLQ_OK) return st;
     if ((st = make_sf_tmap(&tm.sfx_hi, a_hi_sf, g.hi_stages, 1, 1)) != PLQ_OK) return st;
   }
-  if (gt_max_clusters(1) < 1) return PLQ_ERR_CUDA;     // also sets the kernel's shared-memory attribute
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kGtThreads, 1, 1);
-  cfg.dynamicSmemBytes = kGtSmemBytes;
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  // Programmatic dependent launch: this kernel may start while the previous one in the stream drains; it
-  // touches nothing that depends on earlier work before its griddepcontrol.wait.
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = static_cast<unsigned>(slices);
-  attr[1].val.clusterDim.y = 1;
-  attr[1].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_tc_kernel, tm, g));
-  return PLQ_OK;
+  return m <= 8 ? gt_launch<8>(tm, g, n, k_lo, k_hi, static_cast<cudaStream_t>(stream))
+                : gt_launch<16>(tm, g, n, k_lo, k_hi, static_cast<cudaStream_t>(stream));
 }

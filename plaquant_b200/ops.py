@@ -185,7 +185,7 @@ def gemv(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
 
 
 def gemv_tc(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode path on the tensor cores, a.rows <= 8; both operands with the tiled scale layout of the GEMM."""
+    """Decode path on the tensor cores, a.rows <= 16; both operands with the tiled scale layout of the GEMM."""
     _check_pair(a, b, SF_TILED)
     y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
     with torch.cuda.device(a.device):

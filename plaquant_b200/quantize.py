@@ -130,7 +130,7 @@ class QuantizedLinear:
             pa, lead = self.quantize_input(x, norm_weight, eps), x.shape[:-1]
         if pa.sf_layout == ops.SF_ROWMAJOR:
             y = ops.gemv(pa, self._gemv_w)             # a caller-packed operand in the spec's row-major layout
-        elif pa.rows <= 8:
+        elif pa.rows <= 16:
             y = ops.gemv_tc(pa, self._gemm_w)          # decode: stream the weights once
         else:
             y = ops.mixed_gemm(pa, self._gemm_w)

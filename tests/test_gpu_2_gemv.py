@@ -60,7 +60,7 @@ def test_gemv_argument_errors():
 
 
 # ---- tensor-core GEMV (tiled scale layout, the operands of the fused GEMM) ----------------------
-@pytest.mark.parametrize("m", [1, 2, 4, 8, 3])
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 3, 9, 16])
 @pytest.mark.parametrize("n,k,k_hi", [(256, 4096, 128), (200, 14336, 448), (136, 192, 64), (16, 64, 0),
                                        (128, 128, 128), (1024, 8192, 256), (8, 13952, 64)])
 def test_gemv_tc_against_oracle(m, n, k, k_hi):
@@ -76,12 +76,13 @@ def test_gemv_tc_against_oracle(m, n, k, k_hi):
     assert r <= TOL, r
 
 
+@pytest.mark.parametrize("m", [8, 16])
 @pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
-def test_llama8b_shapes_gemv_tc(n, k):
-    """Full decode shapes at m = 8: agreement with the fused GEMM on the identical operands, a sample of
+def test_llama8b_shapes_gemv_tc(n, k, m):
+    """Full decode shapes at m = 8 and 16: agreement with the fused GEMM on the identical operands, a sample of
     output columns against the oracle, and run-to-run determinism."""
     k_hi = k // 32
-    xc, wc = synth_activation(8, k, seed=42).cuda(), synth_weight(n, k, seed=n // 7 + k).cuda()
+    xc, wc = synth_activation(m, k, seed=42).cuda(), synth_weight(n, k, seed=n // 7 + k).cuda()
     pa = plq.pack(xc, k_hi, hadamard=True, sf_layout="tiled")
     pb = plq.pack(wc, k_hi, hadamard=True, sf_layout="tiled")
     y = plq.gemv_tc(pa, pb)
@@ -97,8 +98,8 @@ def test_llama8b_shapes_gemv_tc(n, k):
 
 
 def test_gemv_tc_argument_errors():
-    x = synth_activation(9, 256, seed=1).cuda()
+    x = synth_activation(17, 256, seed=1).cuda()
     pa = plq.pack(x, 64, sf_layout="tiled")
     with pytest.raises(plq.PlqError) as e:
-        plq.gemv_tc(pa, pa)          # m = 9 > 8
+        plq.gemv_tc(pa, pa)          # m = 17 > 16
     assert e.value.status == -2
