@@ -383,6 +383,8 @@ def main_model(args, rank, local_rank, world):
     clocks = sampler.stop()
     plq.check_device_status()
     ms = e0.elapsed_time(e1) / steps
+    tev = getattr(model, "timing_events", None)
+    phases = {"prefill_ms": tev[0].elapsed_time(tev[1]), "decode_ms": tev[1].elapsed_time(tev[2])} if tev else {}
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -398,7 +400,7 @@ def main_model(args, rank, local_rank, world):
             "metric": "decoder tokens/s (prefill + greedy decode)", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)",
-            "data": "synthetic", "clocks": clocks, "ranks_agree_on_tokens": same,
+            "data": "synthetic", "clocks": clocks, "ranks_agree_on_tokens": same, "last_run_phases": phases,
             "config": {"workload": f"Llama-3-70B architecture, {layers} of 80 layers, random init, batch {batch}, "
                                    f"prefill {prefill} + {decode} greedy decode steps", "parallelism": f"tp{world}"}}),
             flush=True)

@@ -111,32 +111,50 @@ class ResQForwardB200:
         """[RMSNorm] -> Hadamard -> quantise -> packed GEMM / GEMV (reference: forward_pass.py:278-319)."""
         return lin(x, norm_weight=norm_weight, eps=self.cfg.rms_eps)
 
-    def _rope(self, q, k, pos0: int):
+    def _rope_angles(self, pos: torch.Tensor):
+        """cos / sin tables [1, T, 1, head_dim] for float32 positions `pos` [T] (a device tensor, so that a decode
+        step captured in a CUDA graph reads its position from memory)."""
         c = self.cfg
-        t = q.shape[1]
-        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=q.device, dtype=torch.float32) / c.head_dim))
-        ang = torch.outer(torch.arange(pos0, pos0 + t, device=q.device, dtype=torch.float32), inv)
-        cos, sin = torch.cat([ang.cos(), ang.cos()], -1)[None, :, None, :], torch.cat([ang.sin(), ang.sin()], -1)[None, :, None, :]
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=pos.device, dtype=torch.float32) / c.head_dim))
+        ang = torch.outer(pos, inv)
+        return (torch.cat([ang.cos(), ang.cos()], -1)[None, :, None, :],
+                torch.cat([ang.sin(), ang.sin()], -1)[None, :, None, :])
+
+    def _rope(self, q, k, pos: torch.Tensor):
+        c = self.cfg
+        cos, sin = self._rope_angles(pos)
 
         def rot(v):
             v1, v2 = v[..., : c.head_dim // 2], v[..., c.head_dim // 2:]
             return (v.float() * cos + torch.cat([-v2, v1], -1).float() * sin).to(v.dtype)
         return rot(q), rot(k)
 
-    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int) -> torch.Tensor:
+    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int, static: Optional[dict] = None) -> torch.Tensor:
+        """One decoder layer.  Without `static`, keys and values are kept in a growing Python-side cache (prefill,
+        and decode steps of arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...],
+        the device tensors `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position
+        is data, which is what CUDA-graph capture of a decode step needs."""
         c, L = self.cfg, self.layers[li]
         b, t, _ = h.shape
         qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
-        q, k = self._rope(q, k, pos0)
-        if pos0 == 0:
-            self.kv[li] = (k, v)
+        if static is None:
+            q, k = self._rope(q, k, torch.arange(pos0, pos0 + t, device=h.device, dtype=torch.float32))
+            if pos0 == 0:
+                self.kv[li] = (k, v)
+            else:
+                self.kv[li] = (torch.cat([self.kv[li][0], k], 1), torch.cat([self.kv[li][1], v], 1))
+            kk, vv = self.kv[li]
+            attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                  is_causal=(t > 1), enable_gqa=True)
         else:
-            self.kv[li] = (torch.cat([self.kv[li][0], k], 1), torch.cat([self.kv[li][1], v], 1))
-        kk, vv = self.kv[li]
-        attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
-                                              is_causal=(t > 1), enable_gqa=True)
+            q, k = self._rope(q, k, static["pos"].to(torch.float32))
+            kk, vv = static["k"][li], static["v"][li]
+            kk.index_copy_(1, static["pos"], k)
+            vv.index_copy_(1, static["pos"], v)
+            attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                  attn_mask=static["mask"], enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
         h = h + self.ctx.all_reduce(self._quantized_linear(attn, L.o))
         gu = self._quantized_linear(h, L.gate_up, norm_weight=L.ln2)
@@ -153,15 +171,73 @@ class ResQForwardB200:
         for li in range(len(self.layers)):
             h = self._forward_layer(li, h, pos0)
         self.pos = pos0 + input_ids.shape[1]
-        last = rms_norm(h[:, -1], self.final_norm, self.cfg.rms_eps)
-        return last.float() @ self.lm_head.float().T
+        return self._logits(h[:, -1])
+
+    def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
+        """Final norm + unquantised LM head in the model dtype (inference/forward_pass.py:178-181 in the reference)."""
+        last = rms_norm(h_last, self.final_norm, self.cfg.rms_eps)
+        return F.linear(last, self.lm_head).float()
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, steps: int) -> torch.Tensor:
-        """Prefill + `steps` greedy decode steps; returns the generated ids [B, steps]."""
-        out = []
-        nxt = self.forward(input_ids).argmax(-1, keepdim=True)
-        for _ in range(steps):
-            out.append(nxt)
-            nxt = self.forward(nxt, pos0=self.pos).argmax(-1, keepdim=True)
-        return torch.cat(out, 1)
+    def generate(self, input_ids: torch.Tensor, steps: int, use_graph: bool = True) -> torch.Tensor:
+        """Prefill + `steps` greedy decode steps; returns the generated ids [B, steps].
+
+        With `use_graph` the decode step (fixed shapes: caches preallocated for prefill + steps positions, the
+        position and the attention mask held in device memory) is captured once in a CUDA graph and replayed, so
+        a step costs its kernels and not ~2000 Python-side launches."""
+        if not use_graph or steps < 2:
+            out = []
+            nxt = self.forward(input_ids).argmax(-1, keepdim=True)
+            for _ in range(steps):
+                out.append(nxt)
+                nxt = self.forward(nxt, pos0=self.pos).argmax(-1, keepdim=True)
+            return torch.cat(out, 1)
+
+        c, dev = self.cfg, self.device
+        b, t0 = input_ids.shape
+        t_max = t0 + steps
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        nxt = self.forward(input_ids).argmax(-1, keepdim=True)              # eager prefill fills self.kv
+        ev[1].record()
+        st = {"k": [], "v": [], "pos": torch.full((1,), t0, dtype=torch.int64, device=dev),
+              "mask": torch.zeros(1, 1, 1, t_max, dtype=torch.bool, device=dev)}
+        for li in range(len(self.layers)):
+            for name, src in (("k", self.kv[li][0]), ("v", self.kv[li][1])):
+                buf = torch.zeros(b, t_max, self.kv_heads, c.head_dim, dtype=src.dtype, device=dev)
+                buf[:, :t0] = src
+                st[name].append(buf)
+        self.kv = [None] * len(self.layers)
+        tok = nxt.clone()                                                    # [B, 1] current token, updated in place
+        out = torch.zeros(b, steps, dtype=nxt.dtype, device=dev)
+        step_idx = torch.zeros(1, dtype=torch.int64, device=dev)
+        arange = torch.arange(t_max, device=dev)
+
+        def decode_step():
+            out.index_copy_(1, step_idx, tok)
+            st["mask"].copy_((arange <= st["pos"]).view(1, 1, 1, t_max))
+            h = F.embedding(tok, self.embed)
+            for li in range(len(self.layers)):
+                h = self._forward_layer(li, h, 0, static=st)
+            tok.copy_(self._logits(h[:, -1]).argmax(-1, keepdim=True))
+            st["pos"].add_(1)
+            step_idx.add_(1)
+
+        decode_step()                                                        # warm-up (also step 0 of the output)
+        if steps > 1:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                decode_step()                                                # step 1, eager on the capture stream
+                side.synchronize()
+                if steps > 2:
+                    with torch.cuda.graph(graph, stream=side):
+                        decode_step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            for _ in range(steps - 2):                                       # capture does not execute: steps 2 .. steps-1
+                graph.replay()
+        ev[2].record()
+        self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. capture) = ev[1] -> ev[2], once synchronised
+        self.pos = t_max
+        return out

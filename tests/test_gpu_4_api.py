@@ -90,6 +90,8 @@ def test_hadamard_matrix_and_decoder_forward():
     assert torch.equal(logits, model.forward(ids))
     gen = model.generate(ids, 5)
     assert gen.shape == (3, 5)
+    # the CUDA-graph decode (static caches, position as data) and the eager growing-cache decode agree
+    assert torch.equal(gen, model.generate(ids, 5, use_graph=False))
     # incremental decoding reproduces a full forward over the extended sequence
     full = model.forward(torch.cat([ids, gen[:, :1]], 1))
     model.forward(ids)
