@@ -537,21 +537,23 @@ def main_case(args):
         pa = plq.pack(activ(args.m, k), k // 32, hadamard=True, sf_layout="tiled")
         y = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: plq.mixed_gemm(pa, pw, out=y, variant=args.variant)
+        pws = clone_packed(plq, pw, max(2, int(400e6 // pw.nbytes())))
+        rot = [(lambda w=w_: plq.mixed_gemm(pa, w, out=y, variant=args.variant)) for w_ in pws]
         work, unit = 2.0 * args.m * n * k, "TFLOP/s"
     flush = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
     for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize()
     ms = time_cuda(torch, fn, args.steps, flush)
-    if args.case in ("gemv", "gemv_tc"):
+    if args.case in ("gemv", "gemv_tc", "gemm"):
         ms_rot = time_rotating(torch, rot, max(1, args.steps // 4))
     plq.check_device_status()
     rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
     line = {"case": args.case, "shape": name, "m": args.m, "us_per_launch": ms * 1e3, "rate": rate, "unit": unit,
             "work": work}
-    if args.case in ("gemv", "gemv_tc"):
+    if args.case in ("gemv", "gemv_tc", "gemm"):
         line["us_back_to_back"] = ms_rot * 1e3
-        line["rate_back_to_back"] = work / (ms_rot * 1e-3) / 1e9
+        line["rate_back_to_back"] = work / (ms_rot * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
     print(json.dumps(line), flush=True)
 
 

@@ -476,14 +476,22 @@ extern "C" int plq_mixed_gemm_variant(const void* a_lo_codes, const void* a_lo_s
   g.wide_store = (reinterpret_cast<uintptr_t>(y_bf16) % 32 == 0 && ldy % 16 == 0) ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (variant == PLQ_GEMM_AUTO) {
-    // A CTA pair needs 30 % fewer bytes from L2 per MMA, which is what bounds large problems;
-    // small ones are better off with more, smaller tiles.
+    // The kernel is bound by the bytes a CTA pulls from L2 per K stage (38 KB for a CTA of a pair, 54 KB
+    // for a 128 x 256 tile, 36 KB for a 128 x 128 tile), so the cheapest shape is the one with the smallest
+    // (waves over the SMs) x (bytes per stage); ties go to the larger tile.
     const int sms = sm_count();
+    const int64_t mt = (m + 127) / 128;
     const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    const int64_t wide_tiles = ((m + 127) / 128) * ((n + 255) / 256);
-    if (n >= 256 && pair_tiles >= sms / 2) variant = PLQ_GEMM_PAIR_256x256;
-    else if (n >= 256 && (wide_tiles >= sms || n % 256 == 0)) variant = PLQ_GEMM_128x256;
-    else variant = PLQ_GEMM_128x128;
+    const int64_t wide_tiles = mt * ((n + 255) / 256);
+    const int64_t small_tiles = mt * ((n + 127) / 128);
+    const int64_t pair_slots = sms / 2 > 0 ? sms / 2 : 1;
+    const int64_t cost_pair = ((pair_tiles + pair_slots - 1) / pair_slots) * 38;
+    const int64_t cost_wide = ((wide_tiles + sms - 1) / sms) * 54;
+    const int64_t cost_small = ((small_tiles + sms - 1) / sms) * 36;
+    variant = PLQ_GEMM_PAIR_256x256;
+    int64_t best = cost_pair;
+    if (cost_wide < best) { variant = PLQ_GEMM_128x256; best = cost_wide; }
+    if (cost_small < best || n < 256) variant = PLQ_GEMM_128x128;
   }
   if (variant == PLQ_GEMM_128x128) return launch_gemm<128, 1>(ptrs, g, s);
   if (variant == PLQ_GEMM_128x256) return launch_gemm<256, 1>(ptrs, g, s);
