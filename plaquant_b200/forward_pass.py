@@ -120,16 +120,16 @@ class ResQForwardB200:
         return (torch.cat([ang.cos(), ang.cos()], -1)[None, :, None, :],
                 torch.cat([ang.sin(), ang.sin()], -1)[None, :, None, :])
 
-    def _rope(self, q, k, pos: torch.Tensor):
+    def _rope(self, q, k, cos_sin):
         c = self.cfg
-        cos, sin = self._rope_angles(pos)
+        cos, sin = cos_sin
 
         def rot(v):
             v1, v2 = v[..., : c.head_dim // 2], v[..., c.head_dim // 2:]
             return (v.float() * cos + torch.cat([-v2, v1], -1).float() * sin).to(v.dtype)
         return rot(q), rot(k)
 
-    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int, static: Optional[dict] = None) -> torch.Tensor:
+    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int, cos_sin, static: Optional[dict] = None) -> torch.Tensor:
         """One decoder layer.  Without `static`, keys and values are kept in a growing Python-side cache (prefill,
         and decode steps of arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...],
         the device tensors `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position
@@ -140,7 +140,7 @@ class ResQForwardB200:
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
         if static is None:
-            q, k = self._rope(q, k, torch.arange(pos0, pos0 + t, device=h.device, dtype=torch.float32))
+            q, k = self._rope(q, k, cos_sin)
             if pos0 == 0:
                 self.kv[li] = (k, v)
             else:
@@ -149,7 +149,7 @@ class ResQForwardB200:
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   is_causal=(t > 1), enable_gqa=True)
         else:
-            q, k = self._rope(q, k, static["pos"].to(torch.float32))
+            q, k = self._rope(q, k, cos_sin)
             kk, vv = static["k"][li], static["v"][li]
             kk.index_copy_(1, static["pos"], k)
             vv.index_copy_(1, static["pos"], v)
@@ -168,8 +168,10 @@ class ResQForwardB200:
         if pos0 == 0:
             self.kv = [None] * len(self.layers)
         h = F.embedding(input_ids, self.embed)
+        t = input_ids.shape[1]
+        cos_sin = self._rope_angles(torch.arange(pos0, pos0 + t, device=h.device, dtype=torch.float32))   # once per pass
         for li in range(len(self.layers)):
-            h = self._forward_layer(li, h, pos0)
+            h = self._forward_layer(li, h, pos0, cos_sin)
         self.pos = pos0 + input_ids.shape[1]
         return self._logits(h[:, -1])
 
@@ -217,8 +219,9 @@ class ResQForwardB200:
             out.index_copy_(1, step_idx, tok)
             st["mask"].copy_((arange <= st["pos"]).view(1, 1, 1, t_max))
             h = F.embedding(tok, self.embed)
+            cos_sin = self._rope_angles(st["pos"].to(torch.float32))
             for li in range(len(self.layers)):
-                h = self._forward_layer(li, h, 0, static=st)
+                h = self._forward_layer(li, h, 0, cos_sin, static=st)
             tok.copy_(self._logits(h[:, -1]).argmax(-1, keepdim=True))
             st["pos"].add_(1)
             step_idx.add_(1)
