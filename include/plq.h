@@ -97,6 +97,28 @@ PLQ_API int plq_rmsnorm_pack(const void* x_bf16, const void* gamma_bf16, float e
                      void* stream);
 
 /*
+ * plq_pack fused with the element-wise step that produces its input in the decoder's MLP:
+ * quantises bf16(bf16(SiLU(gate)) * up), gate and up being bf16 [rows, k] with row stride `ld`
+ * elements (ld % 8 == 0; the two halves of one gate_up output: up = gate + k).  Both roundings of
+ * the two PyTorch ops it replaces are kept.  Replaces `F.silu(gate) * up` followed by the
+ * rotation + quantiser of down_proj, inference/forward_pass.py:266-269.
+ */
+PLQ_API int plq_silu_mul_pack(const void* gate_bf16, const void* up_bf16, int64_t ld, int64_t rows, int64_t k,
+                              int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf, void* hi_codes,
+                              void* hi_sf, int sf_layout, void* stream);
+
+/*
+ * plq_rmsnorm_pack fused with the residual add in front of it: h = bf16(residual + x) (one rounding,
+ * as torch's bf16 add) is written to h_out_bf16 [rows, k] (may alias residual_bf16 or x_bf16) and
+ * then normalised, rotated and quantised.  Replaces `x = residual + attn_out; x = rms_norm(x, ln2)`
+ * and the quantiser of the next linear, inference/forward_pass.py:258-264.
+ */
+PLQ_API int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf16, void* h_out_bf16,
+                                 const void* gamma_bf16, float eps, int64_t rows, int64_t k, int64_t k_hi,
+                                 int hadamard, void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf,
+                                 int sf_layout, void* stream);
+
+/*
  * Dequantise a packed matrix back to bf16 [rows, k_lo + k_hi] (= the fake quantiser's return
  * value, promix/quantize/quant_utils.py:750-751, :706-707).
  */

@@ -331,3 +331,21 @@ def linear(px: dict, pw: dict) -> np.ndarray:
     """Y = deq(X) . deq(W)^T in float32 ("dequantise, then float matmul", the parity form of
     tests/test_mixed_gemm.py:149-168 in the reference)."""
     return dequant_mixed(px) @ dequant_mixed(pw).T
+
+
+# ----------------------------------------------------------------------------------------
+# Element-wise steps that the fused pack entry points absorb (inference/forward_pass.py:258-269)
+# ----------------------------------------------------------------------------------------
+def add_bf16(residual: np.ndarray, x: np.ndarray) -> np.ndarray:
+    """bf16 + bf16 as PyTorch computes it: exact float32 sum, one rounding to bf16 (returned as float32)."""
+    return round_to_bf16(np.asarray(residual, dtype=F32) + np.asarray(x, dtype=F32))
+
+
+def silu_mul_bf16(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """F.silu(gate) * up on bf16 tensors: x / (1 + exp(-x)) in float32 rounded to bf16, then the product rounded
+    to bf16.  The float32 exponential of numpy and of the GPU may differ in the last place, which survives the
+    rounding to bf16 for about one element in 10^4: comparisons against this function allow for that."""
+    g = np.asarray(gate, dtype=F32)
+    with np.errstate(over="ignore"):
+        s = round_to_bf16(g / (F32(1.0) + np.exp(-g, dtype=F32)))
+    return round_to_bf16(s * np.asarray(up, dtype=F32))

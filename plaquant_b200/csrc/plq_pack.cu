@@ -17,7 +17,10 @@
 namespace plq {
 
 struct PackArgs {
-  const uint4* x;        // bf16 [rows, k]
+  const uint4* x;        // bf16 [rows, k], row stride ldx8 * 8 elements
+  const uint4* x2;       // prologue 1: the "up" half, same stride as x; prologue 2: the residual [rows, k], contiguous
+  uint4* h_out;          // prologue 2: bf16 [rows, k], receives residual + x
+  int ldx8;              // row stride of x (and of x2 in prologue 1) in 16-byte units
   const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
   float eps;
   float inv_k;           // unused (division is done exactly); kept for layout stability
@@ -30,7 +33,10 @@ struct PackArgs {
   int lo_chunks, hi_chunks;  // chunks per 128-row group in the tiled layouts
 };
 
-template <bool NORM, bool HAD>
+// PRO selects what is quantised: 0 = x; 1 = SiLU(x) * x2 (gate and up halves of the MLP, rounded to bf16 after
+// the activation and after the product like the two PyTorch ops they replace, inference/forward_pass.py:266
+// in the reference); 2 = x2 + x (residual add, one rounding, also written to h_out: forward_pass.py:258-262).
+template <int PRO, bool NORM, bool HAD>
 __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   // A consumer launched with programmatic stream serialisation (the decode GEMV) may set itself up and
   // prefetch its weights while this kernel runs; it waits for this grid's completion before reading the codes.
@@ -45,16 +51,43 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   float2 v2[16];
 
   // ---- load: four 16-byte pieces per lane ---------------------------------------------
-  const uint4* xrow = a.x + static_cast<size_t>(row) * (a.k >> 3);
+  const uint4* xrow = a.x + static_cast<size_t>(row) * a.ldx8;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int kk = k0 + 32 * j + 8 * q;
     uint4 w = make_uint4(0, 0, 0, 0);
     if (kk < a.k) w = __ldg(xrow + (kk >> 3));
-    v2[4 * j + 0] = make_float2(bf16lo_to_f32(w.x), bf16hi_to_f32(w.x));
-    v2[4 * j + 1] = make_float2(bf16lo_to_f32(w.y), bf16hi_to_f32(w.y));
-    v2[4 * j + 2] = make_float2(bf16lo_to_f32(w.z), bf16hi_to_f32(w.z));
-    v2[4 * j + 3] = make_float2(bf16lo_to_f32(w.w), bf16hi_to_f32(w.w));
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    if constexpr (PRO == 0) {
+#pragma unroll
+      for (int p = 0; p < 4; ++p) v2[4 * j + p] = make_float2(bf16lo_to_f32(ww[p]), bf16hi_to_f32(ww[p]));
+    } else if constexpr (PRO == 1) {
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (kk < a.k) u = __ldg(a.x2 + static_cast<size_t>(row) * a.ldx8 + (kk >> 3));
+      const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float g0 = bf16lo_to_f32(ww[p]), g1 = bf16hi_to_f32(ww[p]);
+        const uint32_t t = f32x2_to_bf16x2(g0 / (1.0f + expf(-g0)), g1 / (1.0f + expf(-g1)));   // SiLU, to bf16
+        const float2 prod = __fmul2_rn(make_float2(bf16lo_to_f32(t), bf16hi_to_f32(t)),
+                                       make_float2(bf16lo_to_f32(uu[p]), bf16hi_to_f32(uu[p])));
+        const uint32_t b = f32x2_to_bf16x2(prod.x, prod.y);                                       // product, to bf16
+        v2[4 * j + p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
+      }
+    } else {
+      uint4 r = make_uint4(0, 0, 0, 0);
+      if (kk < a.k) r = __ldg(a.x2 + static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3));
+      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+      uint32_t hh[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float2 sum = __fadd2_rn(make_float2(bf16lo_to_f32(rr[p]), bf16hi_to_f32(rr[p])),
+                                      make_float2(bf16lo_to_f32(ww[p]), bf16hi_to_f32(ww[p])));
+        hh[p] = f32x2_to_bf16x2(sum.x, sum.y);
+        v2[4 * j + p] = make_float2(bf16lo_to_f32(hh[p]), bf16hi_to_f32(hh[p]));
+      }
+      if (kk < a.k) a.h_out[static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3)] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+    }
   }
 
   // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
@@ -263,10 +296,13 @@ static int check_pack_args(const void* x, int64_t rows, int64_t k, int64_t k_hi,
   return PLQ_OK;
 }
 
-static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows, int64_t k, int64_t k_hi,
-                       int hadamard, void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout,
-                       void* stream) {
+static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int64_t ldx, const void* gamma, float eps,
+                       int64_t rows, int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
+                       void* hi_codes, void* hi_sf, int sf_layout, void* stream) {
   const bool norm = gamma != nullptr;
+  if (ldx < k || ldx % 8 != 0) return PLQ_ERR_SHAPE;
+  if (rows > 0 && pro != 0 && (!x2 || !aligned16(x2))) return x2 ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
+  if (rows > 0 && pro == 2 && (!h_out || !aligned16(h_out))) return h_out ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
   int st = check_pack_args(x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
   if (st != PLQ_OK) return st;
   if (rows == 0) return PLQ_OK;
@@ -275,6 +311,9 @@ static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows
   if (st != PLQ_OK) return st;
   PackArgs a;
   a.x = static_cast<const uint4*>(x);
+  a.x2 = static_cast<const uint4*>(x2);
+  a.h_out = static_cast<uint4*>(h_out);
+  a.ldx8 = static_cast<int>(ldx / 8);
   a.gamma = static_cast<const uint4*>(gamma);
   a.eps = eps;
   a.inv_k = 0.0f;
@@ -292,10 +331,18 @@ static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows
   const int threads = ((blocks128 * 4 + 31) / 32) * 32;
   const dim3 grid(static_cast<unsigned>(rows));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (norm && hadamard) pack_kernel<true, true><<<grid, threads, 0, s>>>(a);
-  else if (norm) pack_kernel<true, false><<<grid, threads, 0, s>>>(a);
-  else if (hadamard) pack_kernel<false, true><<<grid, threads, 0, s>>>(a);
-  else pack_kernel<false, false><<<grid, threads, 0, s>>>(a);
+  if (pro == 1) {                      // SiLU(gate) * up: no norm in front of the down projection
+    if (norm) return PLQ_ERR_SHAPE;
+    if (hadamard) pack_kernel<1, false, true><<<grid, threads, 0, s>>>(a);
+    else pack_kernel<1, false, false><<<grid, threads, 0, s>>>(a);
+  } else if (pro == 2) {               // residual add, then RMSNorm
+    if (!norm) return PLQ_ERR_NULL;
+    if (hadamard) pack_kernel<2, true, true><<<grid, threads, 0, s>>>(a);
+    else pack_kernel<2, true, false><<<grid, threads, 0, s>>>(a);
+  } else if (norm && hadamard) pack_kernel<0, true, true><<<grid, threads, 0, s>>>(a);
+  else if (norm) pack_kernel<0, true, false><<<grid, threads, 0, s>>>(a);
+  else if (hadamard) pack_kernel<0, false, true><<<grid, threads, 0, s>>>(a);
+  else pack_kernel<0, false, false><<<grid, threads, 0, s>>>(a);
   PLQ_CUDA_TRY(cudaGetLastError());
   return PLQ_OK;
 }
@@ -304,16 +351,32 @@ static int launch_pack(const void* x, const void* gamma, float eps, int64_t rows
 
 extern "C" int plq_pack(const void* x_bf16, int64_t rows, int64_t k, int64_t k_hi, int hadamard, void* lo_codes,
                         void* lo_sf, void* hi_codes, void* hi_sf, int sf_layout, void* stream) {
-  return plq::launch_pack(x_bf16, nullptr, 0.0f, rows, k, k_hi, hadamard, lo_codes, lo_sf, hi_codes, hi_sf,
-                          sf_layout, stream);
+  return plq::launch_pack(0, x_bf16, nullptr, nullptr, k, nullptr, 0.0f, rows, k, k_hi, hadamard, lo_codes, lo_sf,
+                          hi_codes, hi_sf, sf_layout, stream);
 }
 
 extern "C" int plq_rmsnorm_pack(const void* x_bf16, const void* gamma_bf16, float eps, int64_t rows, int64_t k,
                                 int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf, void* hi_codes,
                                 void* hi_sf, int sf_layout, void* stream) {
   if (!gamma_bf16) return PLQ_ERR_NULL;
-  return plq::launch_pack(x_bf16, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes, lo_sf, hi_codes, hi_sf,
-                          sf_layout, stream);
+  return plq::launch_pack(0, x_bf16, nullptr, nullptr, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes, lo_sf,
+                          hi_codes, hi_sf, sf_layout, stream);
+}
+
+extern "C" int plq_silu_mul_pack(const void* gate_bf16, const void* up_bf16, int64_t ld, int64_t rows, int64_t k,
+                                 int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf, void* hi_codes,
+                                 void* hi_sf, int sf_layout, void* stream) {
+  return plq::launch_pack(1, gate_bf16, up_bf16, nullptr, ld, nullptr, 0.0f, rows, k, k_hi, hadamard, lo_codes,
+                          lo_sf, hi_codes, hi_sf, sf_layout, stream);
+}
+
+extern "C" int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf16, void* h_out_bf16,
+                                    const void* gamma_bf16, float eps, int64_t rows, int64_t k, int64_t k_hi,
+                                    int hadamard, void* lo_codes, void* lo_sf, void* hi_codes, void* hi_sf,
+                                    int sf_layout, void* stream) {
+  if (!gamma_bf16) return PLQ_ERR_NULL;
+  return plq::launch_pack(2, x_bf16, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard,
+                          lo_codes, lo_sf, hi_codes, hi_sf, sf_layout, stream);
 }
 
 extern "C" int plq_unpack(const void* lo_codes, const void* lo_sf, const void* hi_codes, const void* hi_sf,

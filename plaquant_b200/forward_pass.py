@@ -4,9 +4,10 @@ RoPE -> attention -> o_proj -> norm -> gate, up -> silu * up -> down_proj, LM he
 
 What runs where.  The hot path of this repository - RMSNorm + rotation + quantise-and-pack and the
 quantised linears - runs on the CUDA library (fused: the two RMSNorms of a layer never produce a
-bf16 tensor, they feed the pack kernel).  Everything the reference also leaves to PyTorch stays in
-PyTorch: embedding, RoPE, scaled-dot-product attention (forward_pass.py:249 there), SiLU, residual
-adds, the final norm and the LM head (forward_pass.py:178-181 there).
+bf16 tensor, they feed the pack kernel, which also absorbs the residual add in front of each norm and
+SiLU(gate) * up in front of the down projection).  Everything else the reference leaves to PyTorch
+stays in PyTorch: embedding, RoPE, scaled-dot-product attention (forward_pass.py:249 there), the final
+norm and the LM head (forward_pass.py:178-181 there).
 
 Tensor parallelism (Megatron): QKV and gate_up are column-parallel (N sharded by heads / by FFN
 columns, no exchange), O and down are row-parallel (K sharded, one all-reduce each), see tp.py.
@@ -129,18 +130,27 @@ class ResQForwardB200:
             return (v.float() * cos + torch.cat([-v2, v1], -1).float() * sin).to(v.dtype)
         return rot(q), rot(k)
 
-    def _forward_layer(self, li: int, h: torch.Tensor, pos0: int, cos_sin, static: Optional[dict] = None) -> torch.Tensor:
-        """One decoder layer.  Without `static`, keys and values are kept in a growing Python-side cache (prefill,
-        and decode steps of arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...],
-        the device tensors `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position
-        is data, which is what CUDA-graph capture of a decode step needs."""
+    def _forward_layer(self, li: int, h: torch.Tensor, delta: Optional[torch.Tensor], pos0: int, cos_sin,
+                       static: Optional[dict] = None):
+        """One decoder layer.  `h` is the residual stream and `delta` the previous layer's MLP output that has
+        not been added to it yet (None for the first layer): the add is fused into this layer's first
+        RMSNorm-quant kernel, and the layer returns its own (h, delta) in the same form.
+
+        Without `static`, keys and values are kept in a growing Python-side cache (prefill, and decode steps of
+        arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...], the device tensors
+        `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position is data, which
+        is what CUDA-graph capture of a decode step needs."""
         c, L = self.cfg, self.layers[li]
         b, t, _ = h.shape
-        qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
+        if delta is None:
+            qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
+        else:   # h += delta; RMSNorm(ln1); rotate; quantise: one kernel
+            h, pa = ops.add_rmsnorm_pack(delta, h, L.ln1, c.rms_eps, self.k_hi_hidden)
+            qkv = L.qkv(pa).view(b, t, -1)
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
+        q, k = self._rope(q, k, cos_sin)
         if static is None:
-            q, k = self._rope(q, k, cos_sin)
             if pos0 == 0:
                 self.kv[li] = (k, v)
             else:
@@ -149,17 +159,17 @@ class ResQForwardB200:
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   is_causal=(t > 1), enable_gqa=True)
         else:
-            q, k = self._rope(q, k, cos_sin)
             kk, vv = static["k"][li], static["v"][li]
             kk.index_copy_(1, static["pos"], k)
             vv.index_copy_(1, static["pos"], v)
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   attn_mask=static["mask"], enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
-        h = h + self.ctx.all_reduce(self._quantized_linear(attn, L.o))
-        gu = self._quantized_linear(h, L.gate_up, norm_weight=L.ln2)
-        act = F.silu(gu[..., : self.ffn]) * gu[..., self.ffn:]
-        return h + self.ctx.all_reduce(self._quantized_linear(act, L.down))
+        o = self.ctx.all_reduce(self._quantized_linear(attn, L.o))
+        h, pa = ops.add_rmsnorm_pack(o, h, L.ln2, c.rms_eps, self.k_hi_hidden)          # h += o; RMSNorm(ln2); quantise
+        gu = L.gate_up(pa)                                                              # [b*t, 2*ffn] = [gate | up]
+        pa = ops.silu_mul_pack(gu, self.k_hi_ffn)                                       # SiLU(gate)*up; rotate; quantise
+        return h, self.ctx.all_reduce(L.down(pa)).view(b, t, -1)
 
     # ---- public ----------------------------------------------------------------------------------
     @torch.no_grad()
@@ -170,10 +180,11 @@ class ResQForwardB200:
         h = F.embedding(input_ids, self.embed)
         t = input_ids.shape[1]
         cos_sin = self._rope_angles(torch.arange(pos0, pos0 + t, device=h.device, dtype=torch.float32))   # once per pass
+        delta = None
         for li in range(len(self.layers)):
-            h = self._forward_layer(li, h, pos0, cos_sin)
+            h, delta = self._forward_layer(li, h, delta, pos0, cos_sin)
         self.pos = pos0 + input_ids.shape[1]
-        return self._logits(h[:, -1])
+        return self._logits(h[:, -1] + delta[:, -1])
 
     def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
         """Final norm + unquantised LM head in the model dtype (inference/forward_pass.py:178-181 in the reference)."""
@@ -220,9 +231,10 @@ class ResQForwardB200:
             st["mask"].copy_((arange <= st["pos"]).view(1, 1, 1, t_max))
             h = F.embedding(tok, self.embed)
             cos_sin = self._rope_angles(st["pos"].to(torch.float32))
+            delta = None
             for li in range(len(self.layers)):
-                h = self._forward_layer(li, h, 0, cos_sin, static=st)
-            tok.copy_(self._logits(h[:, -1]).argmax(-1, keepdim=True))
+                h, delta = self._forward_layer(li, h, delta, 0, cos_sin, static=st)
+            tok.copy_(self._logits(h[:, -1] + delta[:, -1]).argmax(-1, keepdim=True))
             st["pos"].add_(1)
             step_idx.add_(1)
 

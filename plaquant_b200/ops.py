@@ -116,6 +116,50 @@ def pack(x: torch.Tensor, k_hi: int, hadamard: bool = False, sf_layout="tiled",
     return p
 
 
+def silu_mul_pack(gate_up: torch.Tensor, k_hi: int, hadamard: bool = True, sf_layout="tiled",
+                  out: Optional[PackedMatrix] = None) -> PackedMatrix:
+    """SiLU(gate) * up -> [block-Hadamard 128] -> pack, for gate_up[..., 2K] = [gate | up] (bf16): the input of
+    down_proj without the two element-wise passes (inference/forward_pass.py:266-269 in the reference)."""
+    _require_cuda(gate_up, "gate_up")
+    if gate_up.dtype != torch.bfloat16 or gate_up.shape[-1] % 2:
+        raise TypeError("gate_up must be bfloat16 [..., 2K]")
+    k = gate_up.shape[-1] // 2
+    g2 = gate_up.reshape(-1, 2 * k)
+    if not g2.is_contiguous():
+        g2 = g2.contiguous()
+    rows = g2.shape[0]
+    p = out if out is not None else alloc_packed(rows, k, k_hi, sf_layout, gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        st = _lib.lib().plq_silu_mul_pack(_ptr(g2), g2.data_ptr() + 2 * k if rows else None, 2 * k, rows, k, k_hi,
+                                          int(hadamard), _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes),
+                                          _ptr(p.hi_sf), p.sf_layout, _stream(gate_up.device))
+    _lib.check(st)
+    return p
+
+
+def add_rmsnorm_pack(x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float, k_hi: int,
+                     hadamard: bool = True, sf_layout="tiled", out: Optional[PackedMatrix] = None):
+    """h = residual + x (bf16) -> RMSNorm(gamma, eps) -> [block-Hadamard 128] -> pack.  Returns (h, packed):
+    the residual add, the norm and the quantiser of the next linear in one pass
+    (inference/forward_pass.py:258-264 in the reference)."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16 or x.shape != residual.shape:
+        raise TypeError("x and residual must be bfloat16 tensors of one shape")
+    k = x.shape[-1]
+    x2, r2 = x.reshape(-1, k).contiguous(), residual.reshape(-1, k).contiguous()
+    rows = x2.shape[0]
+    h = torch.empty_like(x2)
+    p = out if out is not None else alloc_packed(rows, k, k_hi, sf_layout, x.device)
+    if gamma.dtype != torch.bfloat16 or gamma.numel() != k:
+        raise TypeError("gamma must be bfloat16 [K]")
+    with torch.cuda.device(x.device):
+        st = _lib.lib().plq_add_rmsnorm_pack(_ptr(x2), _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), rows, k,
+                                             k_hi, int(hadamard), _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes),
+                                             _ptr(p.hi_sf), p.sf_layout, _stream(x.device))
+    _lib.check(st)
+    return h.view(x.shape), p
+
+
 def unpack(p: PackedMatrix) -> torch.Tensor:
     """Dequantise to bf16 [rows, K]: the value the reference's fake quantiser returns."""
     y = torch.empty(p.rows, p.k, dtype=torch.bfloat16, device=p.device)
