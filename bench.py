@@ -63,11 +63,18 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "10",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -75,7 +82,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def stop(self):
         if self.proc is None:
@@ -83,7 +90,14 @@ class ClockSampler:
         time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
-        for r in self.rows:
+        rows = self.rows
+        if self.t0 is not None and self.t1 is not None:
+            # nvidia-smi is started before the warm-up (its start-up takes longer than a short timed region);
+            # keep the samples that fall inside the timed region, or, if it was shorter than three sampling
+            # periods, all samples taken under load since the start
+            inside = [r for r in rows if self.t0 <= r[0] <= self.t1 + 0.02]
+            rows = inside if len(inside) >= 3 else rows
+        for _, r in rows:
             try:
                 sm.append(float(r[0])); mx = float(r[1])
             except Exception:
@@ -155,7 +169,7 @@ def config_dict(n_gpus):
 def main_reference(args, rank):
     if rank != 0:
         return
-    steps = max(args.steps, 1)
+    steps = max(min(args.steps, 40), 1)      # a step is ~0.15-0.3 s of host work: keep the arm within a minute or so
     b = run_cpu_sample(steps, min(args.warmup, 2))
     line = {"impl": "reference", "metric": "mixed NVFP4/MXFP8 GEMM TFLOP/s", "value": b["value"], "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": b["ms_per_step"],
@@ -235,18 +249,20 @@ def main_ours(args, rank, local_rank, world):
         return ms
 
     # ---- device-resident timing -------------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     plq.check_device_status()
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         step(record=True)
     e1.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     plq.check_device_status()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
@@ -373,6 +389,7 @@ def main_model(args, rank, local_rank, world):
     sampler = ClockSampler(local_rank)
     sync()
     sampler.start()
+    sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     steps = max(1, min(args.steps, 5))
     e0.record()
@@ -380,6 +397,7 @@ def main_model(args, rank, local_rank, world):
         out = run()
     e1.record()
     sync()
+    sampler.mark_end()
     clocks = sampler.stop()
     plq.check_device_status()
     ms = e0.elapsed_time(e1) / steps
@@ -565,7 +583,7 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="linears", choices=["linears", "model"],
