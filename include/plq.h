@@ -196,16 +196,21 @@ PLQ_API int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf,
  * untouched by any thread.  When n gives fewer 128-row tiles than SMs, a thread-block cluster of up
  * to 8 CTAs shares each tile along K and combines the partial sums through distributed shared
  * memory in a fixed order; no scratch memory is needed and results do not depend on timing.
- * The kernel is launched with programmatic stream serialisation: it may start (set-up, first
- * weight loads) while the previous kernel of the stream drains, and waits for that kernel's
- * completion before reading the activations or writing y.  `dev_status` as for plq_mixed_gemm.
+ * The kernel is launched with programmatic stream serialisation: its set-up may run while the
+ * previous kernel of the stream drains; it waits for that kernel's completion before it reads an
+ * operand or writes y.  With PLQ_GEMV_STATIC_B in `flags` the caller promises that the B operand
+ * (weight codes and scales) was complete before the kernels that precede this call in the stream
+ * were launched - true for weights packed at load time, not for a weight packed by the call just
+ * before - and the first weight loads are issued before that wait (about 10 % on the largest
+ * decode shape).  `dev_status` as for plq_mixed_gemm.
  * Replaces the same reference lines as plq_gemv (the quantised linear at decode batch sizes,
  * promix/quantize/quant_utils.py:389 / inference/forward_pass.py:319).
  */
+#define PLQ_GEMV_STATIC_B 1   /* flags: the B operand is never written by the kernels just before the call */
 PLQ_API int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
                         const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
                         int64_t m, int64_t n, int64_t k_lo, int64_t k_hi,
-                        void* y_bf16, int64_t ldy, int32_t* dev_status, void* stream);
+                        void* y_bf16, int64_t ldy, int32_t* dev_status, int flags, void* stream);
 
 #ifdef __cplusplus
 }

@@ -129,6 +129,7 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_launch_dependents();          // the next kernel in the stream may be launched while this one runs
 
   const int num_tiles = g.tiles_m * g.tiles_n;
   const int k_stages = g.lo_stages + g.hi_stages;
@@ -141,35 +142,39 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     // Producer p takes the K stages whose running index (over all tiles of this CTA) is = p mod 2.
     if (elect_one()) {
       const int pid = warp == 0 ? 0 : 1;
-      int tile = first_tile, ks = pid;
-      while (ks >= k_stages && tile < num_tiles) { ks -= k_stages; tile += tile_step; }
-      uint32_t gs = pid;                  // running stage index: slot = gs % kStages, use count = gs / kStages
-      bool ok = true;
-      while (ok && tile < num_tiles) {
-        // ---- per tile ----
+      // One stage's loads.  In a pair every load of both CTAs is counted on the leader's barrier, which is the
+      // one the MMA issuer waits on; boxes always have their full size (out-of-range parts are zero-filled).
+      auto issue = [&](uint32_t gs, int tile, int ks) {
         const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
         const int mgrp = tm * CG + static_cast<int>(rank);        // this CTA's 128-row group of A
-        const int m0 = mgrp * kBM;
-        const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;
-        // ---- this thread's stages of the tile ----
-        for (; ks < k_stages; ks += kProducers) {
-          const uint32_t slot = gs % C::kStages;
-          ok = mbar_wait_bounded(&empty_bar[slot], ((gs / C::kStages) & 1u) ^ 1u, abort_flag);
+        const uint32_t slot = gs % C::kStages;
+        const bool lo = ks < g.lo_stages;
+        const int kk = lo ? ks : ks - g.lo_stages;
+        const int chunk0 = lo ? kk * 4 : kk;              // NVFP4: one chunk per MMA; MXFP8: one per stage
+        const uint32_t st = smem_base + slot * C::kStageBytes;
+        const uint32_t bar = smem_u32(&full_bar[slot]) & (CG == 2 ? 0xFEFFFFFFu : 0xFFFFFFFFu);
+        if (leader) mbar_arrive_expect_tx(&full_bar[slot], CG * C::kStageBytes);
+        tma_load_2d_cg<CG>(st, lo ? &tm_a_lo : &tm_a_hi, kk * kStageKBytes, mgrp * kBM, bar);
+        tma_load_2d_cg<CG>(st + kABytes, lo ? &tm_b_lo : &tm_b_hi, kk * kStageKBytes,
+                           tn * BN + static_cast<int>(rank) * C::kBRows, bar);
+        tma_load_3d_cg<CG>(st + kABytes + C::kBBytes, lo ? &maps.sfa_lo : &maps.sfa_hi, 0, chunk0, mgrp, bar);
+        tma_load_3d_cg<CG>(st + kABytes + C::kBBytes + C::kSfaBytes, lo ? &maps.sfb_lo : &maps.sfb_hi, 0, chunk0,
+                           tn * C::kSfGroups, bar);
+      };
+      // Stage gs (running over all tiles of this CTA) belongs to producer gs % 2.  Both operands may have been
+      // written by the kernel just before this one (a weight packed right before its first use included), so
+      // nothing is loaded before the programmatic-dependency wait; barrier set-up, tensor-memory allocation
+      // and descriptor prefetch are what overlaps the previous kernel.
+      pdl_wait();
+      bool ok = true;
+      uint32_t gs = pid;
+      int tile = first_tile, ks = pid;
+      while (ks >= k_stages && tile < num_tiles) { ks -= k_stages; tile += tile_step; }
+      while (ok && tile < num_tiles) {
+        for (; ks < k_stages; ks += kProducers, gs += kProducers) {
+          ok = mbar_wait_bounded(&empty_bar[gs % C::kStages], ((gs / C::kStages) & 1u) ^ 1u, abort_flag);
           if (!ok) break;
-          const bool lo = ks < g.lo_stages;
-          const int kk = lo ? ks : ks - g.lo_stages;
-          const int chunk0 = lo ? kk * 4 : kk;              // NVFP4: one chunk per MMA; MXFP8: one per stage
-          const uint32_t st = smem_base + slot * C::kStageBytes;
-          // In a pair every load of both CTAs is counted on the leader's barrier, which is the one the
-          // MMA issuer waits on; boxes always have their full size (out-of-range parts are zero-filled).
-          const uint32_t bar = smem_u32(&full_bar[slot]) & (CG == 2 ? 0xFEFFFFFFu : 0xFFFFFFFFu);
-          if (leader) mbar_arrive_expect_tx(&full_bar[slot], CG * C::kStageBytes);
-          tma_load_2d_cg<CG>(st, lo ? &tm_a_lo : &tm_a_hi, kk * kStageKBytes, m0, bar);
-          tma_load_2d_cg<CG>(st + kABytes, lo ? &tm_b_lo : &tm_b_hi, kk * kStageKBytes, n0, bar);
-          tma_load_3d_cg<CG>(st + kABytes + C::kBBytes, lo ? &maps.sfa_lo : &maps.sfa_hi, 0, chunk0, mgrp, bar);
-          tma_load_3d_cg<CG>(st + kABytes + C::kBBytes + C::kSfaBytes, lo ? &maps.sfb_lo : &maps.sfb_hi, 0, chunk0,
-                             tn * C::kSfGroups, bar);
-          gs += kProducers;
+          issue(gs, tile, ks);
         }
         ks -= k_stages;
         tile += tile_step;
@@ -278,6 +283,7 @@ mixed_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
+    pdl_wait();                                       // the output may still be read by an earlier kernel
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
       const int row = (tm * CG + static_cast<int>(rank)) * kBM + quad * 32 + lane;
@@ -431,13 +437,17 @@ static int launch_gemm(const GemmPtrs& p, GemmArgs& g, cudaStream_t stream) {
   cfg.blockDim = dim3(C::kThreads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: set-up and the first weight loads may overlap the previous kernel's tail;
+  // activations are read and the output written only after griddepcontrol.wait
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tm, g));
   return PLQ_OK;
 }

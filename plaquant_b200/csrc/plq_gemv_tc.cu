@@ -15,9 +15,10 @@
 // No scratch memory in HBM is needed.  Otherwise S = 1 and CTAs loop over whole tiles.
 //
 // Programmatic dependent launch: the kernel is launched so that it may start while the previous
-// kernel in the stream drains.  Barrier set-up, tensor-memory allocation and the first ring fill
-// of WEIGHT bytes (which no earlier kernel produces) happen before griddepcontrol.wait; the
-// activation loads and the output stores after it.
+// kernel in the stream drains.  Barrier set-up, tensor-memory allocation, descriptor prefetch and
+// the cluster handshake happen before griddepcontrol.wait; every load and store after it - except
+// that a caller who declares the weights static (flag PLQ_GEMV_STATIC_B) lets the first ring fill
+// of weight bytes be requested before the wait.
 //
 //   warps 0, 2, 3  producers, stages round-robin (one thread each)
 //   warp 1         MMA issuer: scale chunks shared -> tensor memory, four MMAs per stage
@@ -63,6 +64,7 @@ struct GtArgs {
   int m, n, k_lo, k_hi;
   int lo_stages, hi_stages, lo_chunks;
   int tiles;
+  int static_b;                    // PLQ_GEMV_STATIC_B: weights may be loaded before the dependency wait
 };
 
 // and-reduction of a predicate over the 128 epilogue threads (named barrier 1)
@@ -150,8 +152,6 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
     // ================================ producers ================================
     if (elect_one()) {
       const uint32_t pid = warp == 0 ? 0u : static_cast<uint32_t>(warp - 1);   // warps 0, 2, 3 -> 0, 1, 2
-      const uint32_t total = static_cast<uint32_t>(my_tiles * (ks_end - ks_begin));
-      const uint32_t n_init = min(total, static_cast<uint32_t>(kGtStages));      // stages that fill the empty ring
       auto issue = [&](uint32_t gs, int tile, int ks, bool w_part, bool x_part) {
         const uint32_t slot = gs % kGtStages;
         const bool lo = ks < g.lo_stages;
@@ -169,15 +169,25 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
           tma_load_3d_cg<1>(st + kABytes + kGtXBytes + kGtSfBytes, lo ? &maps.sfx_lo : &maps.sfx_hi, 0, chunk0, 0, bar);
         }
       };
-      // Pass 0: weight codes and weight scales of the first ring fill.  They do not depend on earlier kernels,
-      // so under programmatic dependent launch they are in flight while the previous kernel drains.
-      // Pass 1, after the dependency wait: the activation parts of those stages.  Then the steady state.
-      for (int pass = 0; pass < 2; ++pass) {
-        if (pass == 1) pdl_wait();
-        uint32_t gs = 0;
-        for (int t = 0; t < my_tiles && gs < n_init; ++t)
-          for (int ks = ks_begin; ks < ks_end && gs < n_init; ++ks, ++gs)
-            if (gs % kGtProducers == pid) issue(gs, first_tile + t * tile_step, ks, pass == 0, pass == 1);
+      // By default both operands may have been written by the kernel just before this one (a weight packed right
+      // before its first use included): nothing is loaded before the programmatic-dependency wait.  When the
+      // caller declares the weights static (PLQ_GEMV_STATIC_B), the weight codes and scales of the first ring
+      // fill are requested before the wait - they are in flight while the previous kernel drains - and the
+      // activation parts of those stages after it.
+      uint32_t n_init = 0;
+      if (g.static_b) {
+        n_init = min(static_cast<uint32_t>(my_tiles * (ks_end - ks_begin)), static_cast<uint32_t>(kGtStages));
+        uint32_t gs0 = 0;
+        for (int t = 0; t < my_tiles && gs0 < n_init; ++t)
+          for (int ks = ks_begin; ks < ks_end && gs0 < n_init; ++ks, ++gs0)
+            if (gs0 % kGtProducers == pid) issue(gs0, first_tile + t * tile_step, ks, true, false);
+      }
+      pdl_wait();
+      if (g.static_b) {
+        uint32_t gs0 = 0;
+        for (int t = 0; t < my_tiles && gs0 < n_init; ++t)
+          for (int ks = ks_begin; ks < ks_end && gs0 < n_init; ++ks, ++gs0)
+            if (gs0 % kGtProducers == pid) issue(gs0, first_tile + t * tile_step, ks, false, true);
       }
       bool ok = true;
       uint32_t gs = 0;
@@ -415,7 +425,7 @@ static int gt_launch(const GtMaps& tm, const GtArgs& g, int64_t n, int64_t k_lo,
 extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
                            const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
                            int64_t m, int64_t n, int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy,
-                           int32_t* dev_status, void* stream) {
+                           int32_t* dev_status, int flags, void* stream) {
   using namespace plq;
   if (m < 1 || m > kGtN || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0 || ldy < n) return PLQ_ERR_SHAPE;
   if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
@@ -439,6 +449,7 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
   g.lo_stages = (g.lo_chunks + 3) / 4;
   g.hi_stages = static_cast<int>((k_hi + 127) / 128);
   g.tiles = static_cast<int>((n + kBM - 1) / kBM);
+  g.static_b = (flags & PLQ_GEMV_STATIC_B) ? 1 : 0;
 
   GtMaps tm;
   memset(&tm, 0, sizeof(tm));

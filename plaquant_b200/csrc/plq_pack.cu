@@ -38,9 +38,12 @@ struct PackArgs {
 // in the reference); 2 = x2 + x (residual add, one rounding, also written to h_out: forward_pass.py:258-262).
 template <int PRO, bool NORM, bool HAD>
 __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
-  // A consumer launched with programmatic stream serialisation (the decode GEMV) may set itself up and
-  // prefetch its weights while this kernel runs; it waits for this grid's completion before reading the codes.
+  // Programmatic dependent launch on both sides.  A consumer launched with programmatic stream serialisation
+  // (GEMM, decode GEMV) may set itself up and prefetch its weights while this kernel runs; it waits for this
+  // grid's completion before reading the codes.  This kernel itself may be launched before its predecessor
+  // has finished, and waits here before it reads anything.
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const int q = tid & 3;
@@ -329,21 +332,28 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.hi_chunks = static_cast<int>((k_hi / 32 + 3) / 4);
   const int blocks128 = static_cast<int>((k + 127) / 128);
   const int threads = ((blocks128 * 4 + 31) / 32) * 32;
-  const dim3 grid(static_cast<unsigned>(rows));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  auto launch = [&](void (*kernel)(const PackArgs)) { return cudaLaunchKernelEx(&cfg, kernel, a); };
   if (pro == 1) {                      // SiLU(gate) * up: no norm in front of the down projection
     if (norm) return PLQ_ERR_SHAPE;
-    if (hadamard) pack_kernel<1, false, true><<<grid, threads, 0, s>>>(a);
-    else pack_kernel<1, false, false><<<grid, threads, 0, s>>>(a);
+    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<1, false, true>));
+    else PLQ_CUDA_TRY(launch(pack_kernel<1, false, false>));
   } else if (pro == 2) {               // residual add, then RMSNorm
     if (!norm) return PLQ_ERR_NULL;
-    if (hadamard) pack_kernel<2, true, true><<<grid, threads, 0, s>>>(a);
-    else pack_kernel<2, true, false><<<grid, threads, 0, s>>>(a);
-  } else if (norm && hadamard) pack_kernel<0, true, true><<<grid, threads, 0, s>>>(a);
-  else if (norm) pack_kernel<0, true, false><<<grid, threads, 0, s>>>(a);
-  else if (hadamard) pack_kernel<0, false, true><<<grid, threads, 0, s>>>(a);
-  else pack_kernel<0, false, false><<<grid, threads, 0, s>>>(a);
-  PLQ_CUDA_TRY(cudaGetLastError());
+    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<2, true, true>));
+    else PLQ_CUDA_TRY(launch(pack_kernel<2, true, false>));
+  } else if (norm && hadamard) PLQ_CUDA_TRY(launch(pack_kernel<0, true, true>));
+  else if (norm) PLQ_CUDA_TRY(launch(pack_kernel<0, true, false>));
+  else if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<0, false, true>));
+  else PLQ_CUDA_TRY(launch(pack_kernel<0, false, false>));
   return PLQ_OK;
 }
 

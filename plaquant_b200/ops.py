@@ -228,14 +228,21 @@ def gemv(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
 
 
 
-def gemv_tc(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode path on the tensor cores, a.rows <= 16; both operands with the tiled scale layout of the GEMM."""
+GEMV_STATIC_B = 1
+
+
+def gemv_tc(a: PackedMatrix, b: PackedMatrix, out: Optional[torch.Tensor] = None,
+            static_weights: bool = False) -> torch.Tensor:
+    """Decode path on the tensor cores, a.rows <= 16; both operands with the tiled scale layout of the GEMM.
+    `static_weights`: b was complete long before this call (packed at load time), so the kernel may start
+    fetching it while the previous kernel of the stream is still running."""
     _check_pair(a, b, SF_TILED)
     y = out if out is not None else torch.empty(a.rows, b.rows, dtype=torch.bfloat16, device=a.device)
     with torch.cuda.device(a.device):
         st = _lib.lib().plq_gemv_tc(_ptr(a.lo_codes), _ptr(a.lo_sf), _ptr(a.hi_codes), _ptr(a.hi_sf),
                                     _ptr(b.lo_codes), _ptr(b.lo_sf), _ptr(b.hi_codes), _ptr(b.hi_sf),
                                     a.rows, b.rows, a.k_lo, a.k_hi, _ptr(y), y.stride(0),
-                                    _ptr(status_word(a.device)), _stream(a.device))
+                                    _ptr(status_word(a.device)), GEMV_STATIC_B if static_weights else 0,
+                                    _stream(a.device))
     _lib.check(st)
     return y

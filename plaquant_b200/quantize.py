@@ -131,7 +131,7 @@ class QuantizedLinear:
         if pa.sf_layout == ops.SF_ROWMAJOR:
             y = ops.gemv(pa, self._gemv_w)             # a caller-packed operand in the spec's row-major layout
         elif pa.rows <= 16:
-            y = ops.gemv_tc(pa, self._gemm_w)          # decode: stream the weights once
+            y = ops.gemv_tc(pa, self._gemm_w, static_weights=True)   # decode: stream the weights once (packed at load)
         else:
             y = ops.mixed_gemm(pa, self._gemm_w)
         return y.view(*lead, self.out_features)

@@ -87,6 +87,8 @@ def test_llama8b_shapes_gemv_tc(n, k, m):
     pb = plq.pack(wc, k_hi, hadamard=True, sf_layout="tiled")
     y = plq.gemv_tc(pa, pb)
     assert torch.equal(y, plq.gemv_tc(pa, pb))
+    torch.cuda.synchronize()       # the weights are complete: the early-prefetch variant may be used
+    assert torch.equal(y, plq.gemv_tc(pa, pb, static_weights=True))
     yg = plq.mixed_gemm(pa, pb)
     plq.check_device_status()
     assert rel_l2(f32_of(y), f32_of(yg)) <= TOL
