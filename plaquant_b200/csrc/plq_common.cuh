@@ -122,25 +122,6 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t p
   return ok != 0;
 }
 
-// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
-// Both addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// 2-D tiled TMA load into this CTA only: coordinates (x = innermost, y).
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int32_t x, int32_t y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
-          "r"(smem_u32(smem_dst)),
-      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
 // Tiled TMA loads for kernels that may run as a CTA pair.  CG = 2 uses the pair form of the
 // instruction, whose completion bytes may be counted on an mbarrier of the other CTA of the
 // pair: `bar_addr` is a shared::cluster address (clear bit 24 of a local address to name the
@@ -309,15 +290,6 @@ __device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint32_t a_lo, uint
   else PLQ_TC_MMA_ASM("2", "mxf8f6f4.block_scale");
 }
 #undef PLQ_TC_MMA_ASM
-// 32 lanes x 16 consecutive 32-bit columns from registers (thread i writes lane base + i)
-__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
 // Shared -> tensor memory copy of 32 rows x 128 bit, replicated to the four lane quadrants
 // (for a CTA pair: in both CTAs, each from its own shared memory at the same offset).
 template <int CG>
@@ -333,7 +305,6 @@ __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint32_t de
                  "r"(desc_lo), "r"(desc_hi)
                  : "memory");
 }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).
 __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

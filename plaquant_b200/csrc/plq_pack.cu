@@ -23,7 +23,6 @@ struct PackArgs {
   int ldx8;              // row stride of x (and of x2 in prologue 1) in 16-byte units
   const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
   float eps;
-  float inv_k;           // unused (division is done exactly); kept for layout stability
   int rows, k, k_lo;     // k_hi = k - k_lo
   uint8_t* lo_codes;     // [rows, k_lo/2]
   uint8_t* lo_sf;
@@ -319,7 +318,6 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.ldx8 = static_cast<int>(ldx / 8);
   a.gamma = static_cast<const uint4*>(gamma);
   a.eps = eps;
-  a.inv_k = 0.0f;
   a.rows = static_cast<int>(rows);
   a.k = static_cast<int>(k);
   a.k_lo = static_cast<int>(k - k_hi);
