@@ -95,6 +95,13 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
   if constexpr (NORM) {
     __shared__ float warp_sums[32];
+    uint4 gpre[4];                                      // the norm weights: requested now, needed after the row sum
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kk = k0 + 32 * j + 8 * q;
+      gpre[j] = make_uint4(0, 0, 0, 0);
+      if (kk < a.k) gpre[j] = __ldg(a.gamma + (kk >> 3));
+    }
     float2 s2 = make_float2(0.0f, 0.0f);               // even and odd elements accumulate separately
 #pragma unroll
     for (int p = 0; p < 16; ++p) s2 = __ffma2_rn(v2[p], v2[p], s2);   // v*v is exact for bf16 inputs
@@ -114,10 +121,7 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
     const float2 r2 = make_float2(r, r);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int kk = k0 + 32 * j + 8 * q;
-      uint4 g = make_uint4(0, 0, 0, 0);
-      if (kk < a.k) g = __ldg(a.gamma + (kk >> 3));
-      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      const uint32_t gw[4] = {gpre[j].x, gpre[j].y, gpre[j].z, gpre[j].w};
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
         const float2 y = __fmul2_rn(make_float2(bf16lo_to_f32(gw[p]), bf16hi_to_f32(gw[p])), __fmul2_rn(v2[4 * j + p], r2));
