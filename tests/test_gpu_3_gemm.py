@@ -112,10 +112,12 @@ def test_config0_single_linear_against_reference_fixture(golden_dir):
     assert rel_l2(f32_of(plq.mixed_gemm(pa2, pb)), want) <= TOL
 
 
-def test_prefill_full_size_properties():
-    """M = 8192 on the QKV shape (4096 -> 6144): sampled rows against the oracle, identical rows
-    whatever the M they are computed in (tiles are independent), determinism, clean status."""
-    m, n, k, k_hi = 8192, 6144, 4096, 128
+@pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
+def test_prefill_full_size_properties(n, k):
+    """M = 8192 on the four Llama-3-8B shapes (the down projection runs the banded tile order): sampled rows
+    against the oracle, identical rows whatever the M they are computed in (tiles are independent),
+    determinism, clean status."""
+    m, k_hi = 8192, k // 32
     x = synth_activation(m, k, seed=3000)
     w = synth_weight(n, k, seed=3001)
     pa = plq.pack(x.cuda(), k_hi, hadamard=True, sf_layout="tiled")
@@ -124,7 +126,7 @@ def test_prefill_full_size_properties():
     y2 = plq.mixed_gemm(pa, pb)
     plq.check_device_status()
     assert torch.equal(y1, y2)
-    sel = np.sort(np.random.default_rng(1).choice(m, 24, replace=False))
+    sel = np.sort(np.random.default_rng(1).choice(m, 12, replace=False))
     na, nb = packed_to_numpy(pa), packed_to_numpy(pb)
     sub = {**na, "rows": len(sel), **{key: na[key][sel] for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf")}}
     want = _oracle_bf16(sub, nb)
