@@ -111,3 +111,20 @@ def test_device_reported_timeout_surfaces_as_an_error():
         plq.check_device_status()
     assert e.value.status == 1 and "bounded wait" in str(e.value)
     plq.check_device_status()          # cleared
+
+
+def test_outputs_with_a_row_stride_leave_the_other_columns_alone():
+    """y may be a column block of a wider tensor (ldy > n): GEMM, both GEMVs."""
+    k, k_hi, n = 1024, 64, 384
+    w = synth_weight(n, k, seed=5).cuda()
+    for m, op, layout in ((200, plq.mixed_gemm, "tiled"), (16, plq.gemv_tc, "tiled"), (8, plq.gemv, "rowmajor")):
+        x = synth_activation(m, k, seed=m).cuda()
+        pa = plq.pack(x, k_hi, hadamard=True, sf_layout=layout)
+        pb = plq.pack(w, k_hi, hadamard=True, sf_layout=layout)
+        want = op(pa, pb)
+        wide = torch.full((m, n + 128), 7.0, dtype=torch.bfloat16, device="cuda")
+        got = op(pa, pb, out=wide[:, 64:64 + n])
+        plq.check_device_status()
+        assert got.data_ptr() == wide[:, 64:].data_ptr()
+        assert torch.equal(wide[:, 64:64 + n], want)
+        assert bool((wide[:, :64] == 7.0).all()) and bool((wide[:, 64 + n:] == 7.0).all())
