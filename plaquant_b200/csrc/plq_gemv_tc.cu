@@ -8,8 +8,9 @@
 // activation codes and scales, which come from L2) keeps ~140 KiB per SM in flight.
 //
 // Work split.  A 128-row tile of W is the unit of output.  When there are fewer tiles than half
-// the SMs, each tile is given to a thread-block cluster of S CTAs (S <= 8, tiles * S <= SMs), CTA
-// r taking the r-th slice of the K stages; CTAs 1..S-1 push their float32 partial sums [8, 128]
+// the SMs, each tile is given to a thread-block cluster of S CTAs (S <= 8, all clusters resident
+// at once), CTA r taking the r-th slice of the K stages; CTAs 1..S-1 push their float32 partial
+// sums [8 or 16 activation rows, 128]
 // into CTA 0's shared memory (distributed shared memory, one hop) and arrive on its barrier, and
 // CTA 0 adds them in slice order (a fixed order: results do not depend on timing) and writes bf16.
 // No scratch memory in HBM is needed.  Otherwise S = 1 and CTAs loop over whole tiles.
