@@ -371,7 +371,7 @@ def main_model(args, rank, local_rank, world):
     ctx = tp.TPContext(rank, world, None)
     cfg = LlamaConfig.llama3_70b()
     layers = args.layers or cfg.num_layers
-    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers)
+    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0)
     batch, prefill, decode = args.batch, args.prefill, args.decode
     ids = torch.randint(0, cfg.vocab_size, (batch, prefill), generator=torch.Generator().manual_seed(40)).to(dev)
 
@@ -584,6 +584,8 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--fused-reduce", action="store_true",
+                    help="model workload: decode all-reduces inside the RMSNorm-quant kernel, over peer memory")
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -119,6 +119,29 @@ PLQ_API int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf16, 
                                  int sf_layout, void* stream);
 
 /*
+ * Tensor-parallel form of plq_add_rmsnorm_pack: the all-reduce that follows a row-parallel linear, the residual
+ * add, the RMSNorm and the quantiser of the next linear in one kernel.  x = bf16(sum over the ranks of their
+ * partial outputs), summed in float32 in rank order so that every rank gets the same bits; the partial outputs
+ * are read from the ranks' own buffers over NVLink (peer loads; no library collective, no multicast).
+ *   peer_x_dev      device array [world] of addresses: rank r's bf16 [rows, k] buffer (this rank's own included),
+ *                   each written by the kernel that precedes this call in rank r's stream
+ *   peer_flags_dev  device array [world] of addresses: rank r's int32 flags[world]
+ *   flags, sync     this rank's flags[world] and int32 sync[2], zero before the first call, owned by the library
+ *                   afterwards
+ * Every rank must make the same sequence of calls; call sites must alternate between two sets of x buffers
+ * (a rank may be one call ahead of a peer that is still reading).  A rank that does not show up within the
+ * bounded wait makes the others store PLQ_DEV_TIMEOUT to `dev_status` and finish (their output is then void).
+ * Replaces `dist.all_reduce` + `x = residual + x; x = rms_norm(x, ...)` + the next quantiser in a
+ * tensor-parallel decoder layer (inference/forward_pass.py:258-264 under tensor parallelism).
+ */
+PLQ_API int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev, int32_t* flags,
+                                           int32_t* sync, int world, int rank, const void* residual_bf16,
+                                           void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
+                                           int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
+                                           void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
+                                           void* stream);
+
+/*
  * Dequantise a packed matrix back to bf16 [rows, k_lo + k_hi] (= the fake quantiser's return
  * value, promix/quantize/quant_utils.py:750-751, :706-707).
  */

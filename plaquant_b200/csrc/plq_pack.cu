@@ -21,6 +21,13 @@ struct PackArgs {
   const uint4* x2;       // prologue 1: the "up" half, same stride as x; prologue 2: the residual [rows, k], contiguous
   uint4* h_out;          // prologue 2: bf16 [rows, k], receives residual + x
   int ldx8;              // row stride of x (and of x2 in prologue 1) in 16-byte units
+  // prologue 3 (tensor-parallel): x = sum over the ranks of their [rows, k] buffers, read over NVLink
+  const uint4* const* peer_x;    // device array [world] of buffer addresses (this rank's own included)
+  int* const* peer_flags;        // device array [world]: rank r's int32 flags[world]
+  int* flags;                    // this rank's flags[world]: flags[r] = last call rank r has announced
+  int* sync;                     // this rank's {calls completed, CTAs finished in the current call}
+  int32_t* status;               // receives PLQ_DEV_TIMEOUT if a rank does not show up
+  int world, rank;
   const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
   float eps;
   int rows, k, k_lo;     // k_hi = k - k_lo
@@ -34,7 +41,10 @@ struct PackArgs {
 
 // PRO selects what is quantised: 0 = x; 1 = SiLU(x) * x2 (gate and up halves of the MLP, rounded to bf16 after
 // the activation and after the product like the two PyTorch ops they replace, inference/forward_pass.py:266
-// in the reference); 2 = x2 + x (residual add, one rounding, also written to h_out: forward_pass.py:258-262).
+// in the reference); 2 = x2 + x (residual add, one rounding, also written to h_out: forward_pass.py:258-262);
+// 3 = like 2 with x = bf16(sum over the tensor-parallel ranks of their partial outputs), float32 sum in rank order,
+// read from the peers' memory: the all-reduce after a row-parallel linear, the residual add, the norm and the
+// quantiser of the next linear in one kernel.
 template <int PRO, bool NORM, bool HAD>
 __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   // Programmatic dependent launch on both sides.  A consumer launched with programmatic stream serialisation
@@ -48,6 +58,30 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   const int q = tid & 3;
   const int k0 = (tid >> 2) * 128;                  // first element of this quad's block
   const int lane = tid & 31;
+  if constexpr (PRO == 3) {
+    // Cross-rank handshake.  Call number c = completed calls + 1.  This rank's partial output was written by
+    // the preceding kernel of the stream; block 0 announces it by storing c into flags[rank] of every peer, and
+    // every block waits (bounded) until all peers have announced c in this rank's flags.  Buffers alternate
+    // between two per call site order, so a peer that runs ahead never overwrites what is being read here.
+    const int call = *reinterpret_cast<volatile int*>(a.sync) + 1;
+    if (blockIdx.x == 0 && tid < a.world) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flags[tid] + a.rank), "r"(call) : "memory");
+    }
+    if (tid < a.world) {
+      const long long t0 = clock64();
+      int seen;
+      do {
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(a.flags + tid) : "memory");
+        if (seen - call >= 0) break;
+        if (clock64() - t0 > kWaitLimitCycles) {        // a rank is missing: report and go on (the result is void)
+          atomicExch(a.status, PLQ_DEV_TIMEOUT);
+          break;
+        }
+      } while (true);
+    }
+    __syncthreads();
+  }
   // v2[p] holds elements (2p, 2p+1) of the lane's 32, i.e. e = 8*j + i -> p = 4*j + i/2.  Arithmetic on
   // pairs uses the packed float32x2 instructions of sm_100 (same IEEE rounding per element, half the issue slots).
   float2 v2[16];
@@ -58,7 +92,27 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
   for (int j = 0; j < 4; ++j) {
     const int kk = k0 + 32 * j + 8 * q;
     uint4 w = make_uint4(0, 0, 0, 0);
-    if (kk < a.k) w = __ldg(xrow + (kk >> 3));
+    if constexpr (PRO == 3) {
+      if (kk < a.k) {
+        float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const size_t off = static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3);
+        for (int r = 0; r < a.world; ++r) {             // rank order: every rank computes the same bits
+          uint4 t;
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w)
+                       : "l"(a.peer_x[r] + off)
+                       : "memory");
+          const uint32_t tt[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+          for (int p = 0; p < 4; ++p)
+            acc[p] = __fadd2_rn(acc[p], make_float2(bf16lo_to_f32(tt[p]), bf16hi_to_f32(tt[p])));
+        }
+        w = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
+                       f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
+      }
+    } else {
+      if (kk < a.k) w = __ldg(xrow + (kk >> 3));
+    }
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     if constexpr (PRO == 0) {
 #pragma unroll
@@ -233,6 +287,18 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
       if (k0 + 64 < a.k_lo) *reinterpret_cast<uint32_t*>(p + 4) = w1;
     }
   }
+  if constexpr (PRO == 3) {
+    // the last block to finish closes the call: the counter the next call's handshake is derived from
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(a.sync + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+        a.sync[1] = 0;
+        __threadfence();
+        atomicAdd(a.sync, 1);
+      }
+    }
+  }
 }
 
 // ---- dequantise packed -> bf16 [rows, k]; one thread per 8 elements -------------------------
@@ -302,14 +368,26 @@ static int check_pack_args(const void* x, int64_t rows, int64_t k, int64_t k_hi,
   return PLQ_OK;
 }
 
+struct PeerArgs {
+  const void* const* peer_x;
+  void* const* peer_flags;
+  int32_t* flags;
+  int32_t* sync;
+  int32_t* status;
+  int world, rank;
+};
+
 static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int64_t ldx, const void* gamma, float eps,
                        int64_t rows, int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
-                       void* hi_codes, void* hi_sf, int sf_layout, void* stream) {
+                       void* hi_codes, void* hi_sf, int sf_layout, void* stream, const PeerArgs* peers = nullptr) {
   const bool norm = gamma != nullptr;
   if (ldx < k || ldx % 8 != 0) return PLQ_ERR_SHAPE;
   if (rows > 0 && pro != 0 && (!x2 || !aligned16(x2))) return x2 ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
-  if (rows > 0 && pro == 2 && (!h_out || !aligned16(h_out))) return h_out ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
-  int st = check_pack_args(x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
+  if (rows > 0 && pro >= 2 && (!h_out || !aligned16(h_out))) return h_out ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
+  if (pro == 3 && (!peers || !peers->peer_x || !peers->peer_flags || !peers->flags || !peers->sync || !peers->status))
+    return PLQ_ERR_NULL;
+  if (pro == 3 && (peers->world < 1 || peers->world > 32 || peers->rank < 0 || peers->rank >= peers->world)) return PLQ_ERR_SHAPE;
+  int st = check_pack_args(pro == 3 ? x2 : x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
   if (st != PLQ_OK) return st;
   if (rows == 0) return PLQ_OK;
   if (norm && !aligned16(gamma)) return PLQ_ERR_ALIGN;
@@ -320,6 +398,14 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.x2 = static_cast<const uint4*>(x2);
   a.h_out = static_cast<uint4*>(h_out);
   a.ldx8 = static_cast<int>(ldx / 8);
+  a.peer_x = nullptr; a.peer_flags = nullptr; a.flags = nullptr; a.sync = nullptr; a.status = nullptr;
+  a.world = 1; a.rank = 0;
+  if (peers) {
+    a.peer_x = reinterpret_cast<const uint4* const*>(peers->peer_x);
+    a.peer_flags = reinterpret_cast<int* const*>(peers->peer_flags);
+    a.flags = peers->flags; a.sync = peers->sync; a.status = peers->status;
+    a.world = peers->world; a.rank = peers->rank;
+  }
   a.gamma = static_cast<const uint4*>(gamma);
   a.eps = eps;
   a.rows = static_cast<int>(rows);
@@ -348,6 +434,10 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
     if (norm) return PLQ_ERR_SHAPE;
     if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<1, false, true>));
     else PLQ_CUDA_TRY(launch(pack_kernel<1, false, false>));
+  } else if (pro == 3) {               // all-reduce over peer memory, residual add, then RMSNorm
+    if (!norm) return PLQ_ERR_NULL;
+    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<3, true, true>));
+    else PLQ_CUDA_TRY(launch(pack_kernel<3, true, false>));
   } else if (pro == 2) {               // residual add, then RMSNorm
     if (!norm) return PLQ_ERR_NULL;
     if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<2, true, true>));
@@ -389,6 +479,19 @@ extern "C" int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf1
   if (!gamma_bf16) return PLQ_ERR_NULL;
   return plq::launch_pack(2, x_bf16, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard,
                           lo_codes, lo_sf, hi_codes, hi_sf, sf_layout, stream);
+}
+
+extern "C" int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev, int32_t* flags,
+                                              int32_t* sync, int world, int rank, const void* residual_bf16,
+                                              void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
+                                              int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
+                                              void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
+                                              void* stream) {
+  if (!gamma_bf16) return PLQ_ERR_NULL;
+  if (rows < 1) return PLQ_ERR_SHAPE;               // every rank must launch, or the others wait for it
+  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank};
+  return plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
+                          lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
 }
 
 extern "C" int plq_unpack(const void* lo_codes, const void* lo_sf, const void* hi_codes, const void* hi_sf,

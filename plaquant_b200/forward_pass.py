@@ -64,6 +64,9 @@ class LlamaConfig:
         return cls()
 
 
+_IN_PEER_BUFFER = object()      # marker: a layer's MLP output is waiting, unreduced, in the peer buffer
+
+
 class _Layer:
     __slots__ = ("ln1", "ln2", "qkv", "o", "gate_up", "down")
 
@@ -72,7 +75,7 @@ class ResQForwardB200:
     """Decoder stack with packed weights resident on one GPU (one tensor-parallel rank)."""
 
     def __init__(self, cfg: LlamaConfig, device, ctx: Optional[tp.TPContext] = None, seed: int = 0,
-                 num_layers: Optional[int] = None):
+                 num_layers: Optional[int] = None, fused_reduce_rows: int = 0):
         self.cfg, self.device, self.ctx = cfg, torch.device(device), ctx or tp.TPContext()
         c, r, s = cfg, self.ctx.rank, self.ctx.size
         assert c.num_heads % s == 0 and c.num_kv_heads % s == 0 and c.intermediate_size % (s * 128) == 0
@@ -99,6 +102,9 @@ class ResQForwardB200:
         self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
         self.kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
         self.pos = 0
+        # decode batches of up to `fused_reduce_rows` rows reduce over peer memory inside the RMSNorm-quant kernel
+        self.peer = (tp.PeerReduce(fused_reduce_rows, c.hidden_size, self.device, self.ctx.group)
+                     if fused_reduce_rows > 0 and self.ctx.size > 1 else None)
 
     def _linear(self, n: int, k: int, k_hi: int, g: torch.Generator) -> QuantizedLinear:
         """Random N(0, 0.02) weight [n, k], rotated and packed on the device; only the packed form is kept."""
@@ -142,8 +148,12 @@ class ResQForwardB200:
         is what CUDA-graph capture of a decode step needs."""
         c, L = self.cfg, self.layers[li]
         b, t, _ = h.shape
+        fused = self.peer is not None and b * t <= self.peer.rows      # all-reduce inside the RMSNorm-quant kernel
         if delta is None:
             qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
+        elif delta is _IN_PEER_BUFFER:   # h += sum over ranks of the previous down_proj; RMSNorm(ln1); quantise
+            h, pa = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, L.ln1, c.rms_eps, self.k_hi_hidden)
+            qkv = L.qkv(pa).view(b, t, -1)
         else:   # h += delta; RMSNorm(ln1); rotate; quantise: one kernel
             h, pa = ops.add_rmsnorm_pack(delta, h, L.ln1, c.rms_eps, self.k_hi_hidden)
             qkv = L.qkv(pa).view(b, t, -1)
@@ -165,10 +175,17 @@ class ResQForwardB200:
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   attn_mask=static["mask"], enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
-        o = self.ctx.all_reduce(self._quantized_linear(attn, L.o))
-        h, pa = ops.add_rmsnorm_pack(o, h, L.ln2, c.rms_eps, self.k_hi_hidden)          # h += o; RMSNorm(ln2); quantise
+        if fused:
+            L.o(attn.reshape(b * t, -1), out=self.peer.buffer(b * t))                   # partial sums stay in the peer buffer
+            h, pa = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, L.ln2, c.rms_eps, self.k_hi_hidden)
+        else:
+            o = self.ctx.all_reduce(self._quantized_linear(attn, L.o))
+            h, pa = ops.add_rmsnorm_pack(o, h, L.ln2, c.rms_eps, self.k_hi_hidden)      # h += o; RMSNorm(ln2); quantise
         gu = L.gate_up(pa)                                                              # [b*t, 2*ffn] = [gate | up]
         pa = ops.silu_mul_pack(gu, self.k_hi_ffn)                                       # SiLU(gate)*up; rotate; quantise
+        if fused and li + 1 < len(self.layers):
+            L.down(pa, out=self.peer.buffer(b * t))                                     # reduced by the next layer's first kernel
+            return h, _IN_PEER_BUFFER
         return h, self.ctx.all_reduce(L.down(pa)).view(b, t, -1)
 
     # ---- public ----------------------------------------------------------------------------------

@@ -160,6 +160,31 @@ def add_rmsnorm_pack(x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tenso
     return h.view(x.shape), p
 
 
+def allreduce_add_rmsnorm_pack(peer, rows: int, residual: torch.Tensor, gamma: torch.Tensor, eps: float, k_hi: int,
+                               hadamard: bool = True, sf_layout="tiled", out: Optional[PackedMatrix] = None):
+    """Tensor-parallel add_rmsnorm_pack: x = sum over the ranks of `peer.buffer(rows)` (each rank's partial output
+    of a row-parallel linear, already written on its stream), h = residual + x, RMSNorm, rotation, pack - one
+    kernel reading the peers' memory over NVLink.  `peer` is a tp.PeerReduce; returns (h, packed)."""
+    _require_cuda(residual, "residual")
+    k = residual.shape[-1]
+    r2 = residual.reshape(-1, k).contiguous()
+    if r2.shape[0] != rows or rows > peer.rows or k != peer.k or residual.dtype != torch.bfloat16:
+        raise TypeError("residual must be bfloat16 [rows, k] matching the peer buffers")
+    if gamma.dtype != torch.bfloat16 or gamma.numel() != k:
+        raise TypeError("gamma must be bfloat16 [K]")
+    h = torch.empty_like(r2)
+    p = out if out is not None else alloc_packed(rows, k, k_hi, sf_layout, residual.device)
+    with torch.cuda.device(residual.device):
+        st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
+            _ptr(peer.peer_x[peer.next]), _ptr(peer.peer_flags), _ptr(peer.flags), _ptr(peer.sync), peer.world, peer.rank,
+            _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), rows, k, k_hi, int(hadamard),
+            _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), p.sf_layout,
+            _ptr(status_word(residual.device)), _stream(residual.device))
+    _lib.check(st)
+    peer.next ^= 1
+    return h.view(residual.shape), p
+
+
 def unpack(p: PackedMatrix) -> torch.Tensor:
     """Dequantise to bf16 [rows, K]: the value the reference's fake quantiser returns."""
     y = torch.empty(p.rows, p.k, dtype=torch.bfloat16, device=p.device)

@@ -117,7 +117,8 @@ class QuantizedLinear:
         return ops.pack(x, self.high_bits_length, hadamard=self.online_had, sf_layout="tiled", gamma=norm_weight,
                         eps=eps)
 
-    def forward(self, x, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    def forward(self, x, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: bf16 [..., K] (or an already packed PackedMatrix).  `norm_weight` fuses the preceding
         RMSNorm (inference/forward_pass.py:33-39) into the quantisation kernel."""
         if self.gemm_impl != "b200":
@@ -129,11 +130,11 @@ class QuantizedLinear:
         else:
             pa, lead = self.quantize_input(x, norm_weight, eps), x.shape[:-1]
         if pa.sf_layout == ops.SF_ROWMAJOR:
-            y = ops.gemv(pa, self._gemv_w)             # a caller-packed operand in the spec's row-major layout
+            y = ops.gemv(pa, self._gemv_w, out=out)    # a caller-packed operand in the spec's row-major layout
         elif pa.rows <= 16:
-            y = ops.gemv_tc(pa, self._gemm_w, static_weights=True)   # decode: stream the weights once (packed at load)
+            y = ops.gemv_tc(pa, self._gemm_w, out=out, static_weights=True)   # decode: stream the weights once
         else:
-            y = ops.mixed_gemm(pa, self._gemm_w)
+            y = ops.mixed_gemm(pa, self._gemm_w, out=out)
         return y.view(*lead, self.out_features)
 
     def set_kernel(self, impl: str = "b200"):

@@ -63,3 +63,38 @@ class TPContext:
         if dist.is_available() and dist.is_initialized():
             return cls(dist.get_rank(), dist.get_world_size(), None)
         return cls()
+
+
+class PeerReduce:
+    """Peer-memory plumbing of the fused all-reduce + residual + RMSNorm-quant kernel
+    (`ops.allreduce_add_rmsnorm_pack`): two symmetric bf16 [rows, k] buffers per rank for the partial outputs
+    (call sites alternate between them), a symmetric int32 flag array, a local call counter, and device arrays
+    with every rank's addresses.  Built on torch.distributed's symmetric memory (CUDA IPC / VMM mappings of the
+    other ranks' allocations on one node); the kernel itself only does plain peer loads and flag stores."""
+
+    def __init__(self, rows: int, k: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.rows, self.k, self.device = rows, k, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.x = symm_mem.empty(2, rows, k, dtype=torch.bfloat16, device=self.device)
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=self.device)
+        self.x.zero_()
+        self.flags.zero_()
+        hx = symm_mem.rendezvous(self.x, group)
+        hf = symm_mem.rendezvous(self.flags, group)
+        self._handles = (hx, hf)                         # keep the mappings alive
+        xs = [int(p) for p in hx.buffer_ptrs]
+        fs = [int(p) for p in hf.buffer_ptrs]
+        per_buf = rows * k * 2
+        self.peer_x = [torch.tensor([p + b * per_buf for p in xs], dtype=torch.int64, device=self.device) for b in range(2)]
+        self.peer_flags = torch.tensor(fs, dtype=torch.int64, device=self.device)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.next = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)                               # nobody signals before every rank has zeroed its flags
+
+    def buffer(self, rows: int) -> torch.Tensor:
+        """The [rows, k] view of the buffer the next fused reduction will read: the row-parallel linear writes
+        its output here."""
+        return self.x[self.next, :rows]

@@ -1,0 +1,70 @@
+"""Fused all-reduce + residual add + RMSNorm-quant over peer memory (two or more GPUs of one node): every rank's
+result must equal the CPU restatement bit for bit, call after call, eager and replayed from a CUDA graph."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+plq = pytest.importorskip("plaquant_b200")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, rows, k, k_hi, calls, q):
+    try:
+        import torch.distributed as dist
+        from oracle import formats as F
+        from plaquant_b200 import ops, tp
+        from tests._util import f32_of, packed_to_numpy
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        peer = tp.PeerReduce(16, k, dev)
+        g = torch.Generator().manual_seed(7)                   # same stream on every rank: all partials known to all
+        gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
+        ok = True
+        for c in range(calls):
+            parts = [torch.randn(rows, k, generator=g).to(torch.bfloat16) for _ in range(world)]
+            res = torch.randn(rows, k, generator=g).to(torch.bfloat16)
+            peer.buffer(rows).copy_(parts[rank].to(dev))       # stands for the row-parallel linear's output
+            h, p = ops.allreduce_add_rmsnorm_pack(peer, rows, res.to(dev), gamma.to(dev), 1e-6, k_hi)
+            plq.check_device_status(dev)
+            acc = np.zeros((rows, k), dtype=np.float32)
+            for part in parts:                                  # float32, rank order
+                acc = acc + f32_of(part)
+            want_h = F.add_bf16(f32_of(res), F.round_to_bf16(acc))
+            want = F.prepare_activation(want_h, k_hi, gamma=f32_of(gamma), eps=1e-6, hadamard=True)
+            got = packed_to_numpy(p)
+            ok = ok and np.array_equal(f32_of(h), want_h)
+            ok = ok and all(np.array_equal(got[key], want[key]) for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"))
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, bool(ok), ""))
+    except Exception as exc:  # noqa: BLE001
+        q.put((rank, False, repr(exc)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("rows,k,k_hi", [(16, 8192, 256), (3, 1024, 64)])
+def test_fused_allreduce_add_rmsnorm_pack_bit_exact(rows, k, k_hi):
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, rows, k, k_hi, 5, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
