@@ -584,8 +584,9 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--fused-reduce", action="store_true",
-                    help="model workload: decode all-reduces inside the RMSNorm-quant kernel, over peer memory")
+    ap.add_argument("--nccl-reduce", dest="fused_reduce", action="store_false",
+                    help="model workload: NCCL all-reduces in the decode step instead of the reduction fused into "
+                         "the RMSNorm-quant kernel over peer memory")
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
