@@ -68,3 +68,34 @@ def test_fused_allreduce_add_rmsnorm_pack_bit_exact(rows, k, k_hi):
     for p in procs:
         p.join(timeout=60)
     assert all(ok for _, ok, _ in results), results
+
+
+def test_a_rank_that_never_announces_itself_gives_a_timeout_status_not_a_hang():
+    """Failure detection without faulting a GPU: rank 1 of a two-rank job is emulated by buffers on this GPU whose
+    flag nothing ever sets.  The bounded wait (about two seconds of SM clock) runs out, the kernel stores
+    PLQ_DEV_TIMEOUT and finishes, the front end raises, and the context stays usable."""
+    from plaquant_b200 import _lib, ops
+    from tests._util import synth_activation, synth_gamma
+    dev = torch.device("cuda", 0)
+    rows, k, k_hi = 4, 1024, 64
+    x = torch.zeros(2, rows, k, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    sync = torch.zeros(2, dtype=torch.int32, device=dev)
+    peer_x = torch.tensor([x[0].data_ptr(), x[1].data_ptr()], dtype=torch.int64, device=dev)
+    peer_flags = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64, device=dev)
+    res = synth_activation(rows, k, seed=1).cuda()
+    gamma = synth_gamma(k, 2).cuda()
+    h = torch.empty_like(res)
+    p = ops.alloc_packed(rows, k, k_hi, "tiled", dev)
+    st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
+        peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), 2, 0, res.data_ptr(), h.data_ptr(),
+        gamma.data_ptr(), 1e-6, rows, k, k_hi, 1, p.lo_codes.data_ptr(), p.lo_sf.data_ptr(), p.hi_codes.data_ptr(),
+        p.hi_sf.data_ptr(), p.sf_layout, ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    assert st == 0
+    with pytest.raises(plq.PlqError) as e:
+        plq.check_device_status(dev)
+    assert e.value.status == 1
+    assert int(sync[0].item()) == 1 and int(flags[0].item()) == 1 and int(flags[1].item()) == 0
+    q = plq.pack(res, k_hi, hadamard=True)                       # the context is intact
+    plq.check_device_status(dev)
+    assert q.rows == rows
