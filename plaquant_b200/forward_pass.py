@@ -10,7 +10,10 @@ stays in PyTorch: embedding, RoPE, scaled-dot-product attention (forward_pass.py
 norm and the LM head (forward_pass.py:178-181 there).
 
 Tensor parallelism (Megatron): QKV and gate_up are column-parallel (N sharded by heads / by FFN
-columns, no exchange), O and down are row-parallel (K sharded, one all-reduce each), see tp.py.
+columns, no exchange), O and down are row-parallel (K sharded, one all-reduce each), see tp.py.  With
+`fused_reduce_rows` > 0, decode batches of up to that many rows do not call NCCL for those all-reduces:
+the row-parallel GEMV writes its partial output into a peer-visible buffer and the following
+RMSNorm-quant kernel sums the ranks' buffers over NVLink itself (ops.allreduce_add_rmsnorm_pack).
 Weights are random-initialised per layer from a seed (no checkpoints are available offline).
 """
 from __future__ import annotations
