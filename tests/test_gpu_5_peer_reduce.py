@@ -99,3 +99,44 @@ def test_a_rank_that_never_announces_itself_gives_a_timeout_status_not_a_hang():
     q = plq.pack(res, k_hi, hadamard=True)                       # the context is intact
     plq.check_device_status(dev)
     assert q.rows == rows
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sum_over_emulated_ranks_on_one_gpu(world):
+    """The arithmetic and the handshake for `world` ranks with one GPU: the other ranks' buffers live on this GPU
+    and their announcements are written from the host before each call (call numbers 1, 2, 3)."""
+    from oracle import formats as F
+    from plaquant_b200 import _lib, ops
+    from tests._util import f32_of, packed_to_numpy, synth_activation, synth_gamma
+    dev = torch.device("cuda", 0)
+    rows, k, k_hi = 5, 2048, 64
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    sync = torch.zeros(2, dtype=torch.int32, device=dev)
+    peer_flags = torch.tensor([flags.data_ptr()] * world, dtype=torch.int64, device=dev)
+    gamma = synth_gamma(k, 2)
+    gamma_d = gamma.cuda()
+    for call in (1, 2, 3):
+        parts = [synth_activation(rows, k, seed=100 * call + r).cuda() for r in range(world)]
+        res = synth_activation(rows, k, seed=100 * call + 50)
+        res_d = res.cuda()                                       # named: a temporary would be freed before the kernel runs
+        peer_x = torch.tensor([p.data_ptr() for p in parts], dtype=torch.int64, device=dev)
+        flags[1:world] = call                                   # "ranks 1.. have announced this call"
+        h = torch.empty(rows, k, dtype=torch.bfloat16, device=dev)
+        p = ops.alloc_packed(rows, k, k_hi, "rowmajor", dev)
+        st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
+            peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, res_d.data_ptr(),
+            h.data_ptr(), gamma_d.data_ptr(), 1e-6, rows, k, k_hi, 1, p.lo_codes.data_ptr(), p.lo_sf.data_ptr(),
+            p.hi_codes.data_ptr(), p.hi_sf.data_ptr(), p.sf_layout, ops.status_word(dev).data_ptr(),
+            torch.cuda.current_stream(dev).cuda_stream)
+        assert st == 0
+        plq.check_device_status(dev)
+        assert int(sync[0].item()) == call and int(flags[0].item()) == call
+        acc = np.zeros((rows, k), dtype=np.float32)
+        for part in parts:
+            acc = acc + f32_of(part)
+        want_h = F.add_bf16(f32_of(res), F.round_to_bf16(acc))
+        assert np.array_equal(f32_of(h), want_h)
+        want = F.prepare_activation(want_h, k_hi, gamma=f32_of(gamma), eps=1e-6, hadamard=True)
+        got = packed_to_numpy(p)
+        for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
+            assert np.array_equal(got[key], want[key]), key
