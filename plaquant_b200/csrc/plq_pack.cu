@@ -88,28 +88,51 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
 
   // ---- load: four 16-byte pieces per lane ---------------------------------------------
   const uint4* xrow = a.x + static_cast<size_t>(row) * a.ldx8;
+  uint4 wsum[PRO == 3 ? 4 : 1];
+  if constexpr (PRO == 3) {
+    // x = bf16(sum over the ranks), float32 in rank order (every rank computes the same bits).  The peer loads
+    // of two of the lane's four pieces are all issued before any of them is used: two NVLink round trips per
+    // lane instead of one per rank and piece.
+#pragma unroll
+    for (int jp = 0; jp < 4; jp += 2) {
+      uint4 t[2][8];
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int kk = k0 + 32 * (jp + jj) + 8 * q;
+        const size_t off = static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          t[jj][r] = make_uint4(0, 0, 0, 0);
+          if (r < a.world && kk < a.k)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(t[jj][r].x), "=r"(t[jj][r].y), "=r"(t[jj][r].z), "=r"(t[jj][r].w)
+                         : "l"(a.peer_x[r] + off)
+                         : "memory");
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < a.world) {
+            const uint32_t tt[4] = {t[jj][r].x, t[jj][r].y, t[jj][r].z, t[jj][r].w};
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+              acc[p] = __fadd2_rn(acc[p], make_float2(bf16lo_to_f32(tt[p]), bf16hi_to_f32(tt[p])));
+          }
+        }
+        wsum[jp + jj] = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
+                                   f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
+      }
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int kk = k0 + 32 * j + 8 * q;
     uint4 w = make_uint4(0, 0, 0, 0);
     if constexpr (PRO == 3) {
-      if (kk < a.k) {
-        float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        const size_t off = static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3);
-        for (int r = 0; r < a.world; ++r) {             // rank order: every rank computes the same bits
-          uint4 t;
-          asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w)
-                       : "l"(a.peer_x[r] + off)
-                       : "memory");
-          const uint32_t tt[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-          for (int p = 0; p < 4; ++p)
-            acc[p] = __fadd2_rn(acc[p], make_float2(bf16lo_to_f32(tt[p]), bf16hi_to_f32(tt[p])));
-        }
-        w = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
-                       f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
-      }
+      w = wsum[j];
     } else {
       if (kk < a.k) w = __ldg(xrow + (kk >> 3));
     }
@@ -386,7 +409,7 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   if (rows > 0 && pro >= 2 && (!h_out || !aligned16(h_out))) return h_out ? PLQ_ERR_ALIGN : PLQ_ERR_NULL;
   if (pro == 3 && (!peers || !peers->peer_x || !peers->peer_flags || !peers->flags || !peers->sync || !peers->status))
     return PLQ_ERR_NULL;
-  if (pro == 3 && (peers->world < 1 || peers->world > 32 || peers->rank < 0 || peers->rank >= peers->world)) return PLQ_ERR_SHAPE;
+  if (pro == 3 && (peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world)) return PLQ_ERR_SHAPE;
   int st = check_pack_args(pro == 3 ? x2 : x, rows, k, k_hi, hadamard, norm, lo_codes, lo_sf, hi_codes, hi_sf, sf_layout);
   if (st != PLQ_OK) return st;
   if (rows == 0) return PLQ_OK;
