@@ -1,0 +1,41 @@
+"""NVFP4 / MXFP8 key and value cache on top of the quantise-and-pack kernel.
+
+The reference quantises keys after RoPE: Hadamard over the head dimension, then its activation quantiser on
+per-head rows `k.view(-1, head_dim)` with the last `high_bits_length` channels of every head in the
+high-precision format (promix/quantize/kv_quant.py:244-279, `k_groupsize != -1` branch; the FP configs
+`promix/configs/*-kv4.yaml` name the formats).  With head_dim = 128 that is exactly one row of the pack kernel
+per (token, head): block-Hadamard(128), NVFP4 codes + E4M3 scales for the first 128 - k_hi channels, MXFP8 codes +
+E8M0 scales for the last k_hi.  The packed cache holds 0.5625 byte per NVFP4 element instead of 2; `dequantize`
+returns what the reference's fake quantiser would have put in the cache.  Queries must be rotated by the same
+Hadamard (`rotate_heads`), which leaves q . k unchanged up to quantisation error.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .rotation import get_hadamard_matrix
+
+
+def quantize_heads(x: torch.Tensor, k_hi: int = 0, hadamard: bool = True) -> ops.PackedMatrix:
+    """x: bf16 [..., heads, head_dim] (keys after RoPE, or values) -> packed rows, one per (token, head).
+    head_dim must be 128 for the rotation; k_hi is the MXFP8 channel count per head (the reference's
+    high_bits_length).  The packed formats need (head_dim - k_hi) % 64 == 0 and k_hi % 32 == 0, so with
+    head_dim = 128 the choices are 0 (all NVFP4, the default) and 64; the reference's 0.125 * head_dim = 16
+    does not fill a 32-element MXFP8 block."""
+    d = x.shape[-1]
+    if hadamard and d != 128:
+        raise ValueError("the block-Hadamard rotation of the cache needs head_dim = 128")
+    return ops.pack(x.reshape(-1, d), k_hi, hadamard=hadamard, sf_layout="rowmajor")
+
+
+def dequantize_heads(p: ops.PackedMatrix, shape) -> torch.Tensor:
+    """Packed rows -> bf16 tensor of `shape` ([..., heads, head_dim]); still in the rotated basis."""
+    return ops.unpack(p).view(*shape)
+
+
+def rotate_heads(q: torch.Tensor) -> torch.Tensor:
+    """The same normalised Hadamard(128) on the head dimension of the queries (float32 product, one rounding:
+    inference/quantize.py:447-448 in the reference)."""
+    h = get_hadamard_matrix(q.shape[-1]).to(q.device)
+    return (q.float() @ h).to(q.dtype)

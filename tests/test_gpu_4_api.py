@@ -128,3 +128,24 @@ def test_outputs_with_a_row_stride_leave_the_other_columns_alone():
         assert got.data_ptr() == wide[:, 64:].data_ptr()
         assert torch.equal(wide[:, 64:64 + n], want)
         assert bool((wide[:, :64] == 7.0).all()) and bool((wide[:, 64 + n:] == 7.0).all())
+
+
+@pytest.mark.parametrize("k_hi", [0, 64])
+def test_kv_cache_quantisation_per_head(k_hi):
+    """Keys [batch, tokens, kv_heads, 128] -> packed per-head rows: codes equal the oracle's on the rotated rows,
+    the dequantised cache equals the oracle's fake-quantised values, and q . k survives the common rotation."""
+    from plaquant_b200 import kv_cache
+    k = synth_activation(2 * 9 * 4, 128, seed=21).view(2, 9, 4, 128).cuda()
+    q = synth_activation(2 * 9 * 4, 128, seed=22).view(2, 9, 4, 128).cuda()
+    p = kv_cache.quantize_heads(k, k_hi=k_hi)
+    want = F.prepare_activation(f32_of(k.view(-1, 128)), k_hi, hadamard=True)
+    assert np.array_equal(p.lo_codes.cpu().numpy(), want["lo_codes"]) and np.array_equal(p.lo_sf.cpu().numpy(), want["lo_sf"])
+    if k_hi:
+        assert np.array_equal(p.hi_codes.cpu().numpy(), want["hi_codes"]) and np.array_equal(p.hi_sf.cpu().numpy(), want["hi_sf"])
+    kd = kv_cache.dequantize_heads(p, k.shape)
+    assert np.array_equal(f32_of(kd.view(-1, 128)), F.round_to_bf16(F.dequant_mixed(want)))
+    s_ref = torch.einsum("bthd,bshd->bhts", q.float(), k.float())
+    s_q = torch.einsum("bthd,bshd->bhts", kv_cache.rotate_heads(q).float(), kd.float())
+    s_rot = torch.einsum("bthd,bshd->bhts", kv_cache.rotate_heads(q).float(), kv_cache.rotate_heads(k).float())
+    assert rel_l2(s_rot.cpu().numpy(), s_ref.cpu().numpy()) < 1e-2     # the common rotation leaves the scores alone
+    assert rel_l2(s_q.cpu().numpy(), s_ref.cpu().numpy()) < 0.35       # 4-bit keys with x20 outlier channels
