@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[3], the one the headline metric is quoted on): prefill with
+Workload (the configuration the headline metric is quoted on): prefill with
 M = 8192 tokens through the four Llama-3-8B linear shapes.  One step =
     RMSNorm + Hadamard + pack of X[8192,4096]  -> fused mixed GEMM 4096 -> 6144   (QKV)
     Hadamard + pack of X[8192,4096]            -> fused mixed GEMM 4096 -> 4096   (O)
