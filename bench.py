@@ -539,6 +539,12 @@ def main_case(args):
         pa = plq.alloc_packed(4096, 4096, 128, "tiled", dev)
         fn = lambda: plq.pack(x, 128, hadamard=True, gamma=gamma, eps=1e-6, out=pa)
         work, unit = 2 * 4096 * 4096 + 2 * 4096 + 4096 * 2364, "GB/s"
+    elif args.case == "silu_pack":
+        f = 14336                                           # Llama-3-8B FFN width: gate_up output [m, 2 f] -> down_proj input
+        gu = activ(args.m, 2 * f)
+        pa = plq.alloc_packed(args.m, f, f // 32, "tiled", dev)
+        fn = lambda: plq.silu_mul_pack(gu, f // 32, out=pa)
+        work, unit = args.m * (2 * f * 2 + pa.nbytes() // args.m), "GB/s"
     elif args.case in ("gemv", "gemv_tc"):
         layout, op = (("rowmajor", plq.gemv) if args.case == "gemv" else
                       ("tiled", lambda a_, b_, out: plq.gemv_tc(a_, b_, out=out, static_weights=True)))
@@ -578,7 +584,7 @@ def main_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["pack", "gemv", "gemv_tc", "gemm"],
+    ap.add_argument("--case", default=None, choices=["pack", "silu_pack", "gemv", "gemv_tc", "gemm"],
                     help="run one kernel on one fixed case instead of the full step")
     ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
     ap.add_argument("--m", type=int, default=None)
