@@ -6,8 +6,9 @@
  * asynchronously on that stream and returns an int status: 0 = ok, negative = argument or
  * host-side error detected before anything was launched (see plq_status_string), positive
  * values are only ever written by a kernel into the caller's status word.  The caller owns
- * and allocates every buffer, outputs and workspaces included; the library never allocates,
- * frees or keeps device memory.  There is no CPU fallback: on a device that is not sm_100
+ * and allocates every buffer, outputs and workspaces included; the library never allocates
+ * or frees device memory (plq_gemv_static_scratch uses an array built into the library image
+ * instead of a caller's workspace).  There is no CPU fallback: on a device that is not sm_100
  * the calls return PLQ_ERR_ARCH.
  *
  * Packed operand ("rows x K" matrix whose last K_hi columns are the outlier subspace):
