@@ -123,6 +123,8 @@ def run_cpu_sample(steps: int, warmup: int):
     import numpy as np
     import torch
     from oracle import cport
+    # all host threads, whatever a launcher exported for its workers (torchrun sets OMP_NUM_THREADS=1)
+    cport.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
 
     def bits(t):
         return t.contiguous().view(torch.int16).numpy().view(np.uint16)

@@ -20,6 +20,8 @@ def lib():
         h.plqo_dequant.argtypes = [vp, vp, vp, vp, i64, i32, i32, vp]
         h.plqo_matmul_nt.argtypes = [vp, vp, i64, i64, i32, vp]
         h.plqo_num_threads.restype = i32
+        h.plqo_set_num_threads.argtypes = [i32]
+        h.plqo_set_num_threads.restype = None
         _lib = h
     return _lib
 
@@ -54,6 +56,11 @@ def linear(px: dict, pw: dict) -> np.ndarray:
     y = np.empty((a.shape[0], b.shape[0]), np.float32)
     lib().plqo_matmul_nt(_p(a), _p(b), a.shape[0], b.shape[0], a.shape[1], _p(y))
     return y
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP team size of the port (launchers such as torchrun export OMP_NUM_THREADS=1 to their workers)."""
+    lib().plqo_set_num_threads(int(n))
 
 
 def num_threads() -> int:
