@@ -25,7 +25,7 @@ from typing import List, Optional, Tuple
 import torch
 import torch.nn.functional as F
 
-from . import ops, tp
+from . import kv_cache, ops, tp
 from .quantize import QuantizedLinear
 from .rotation import get_hadamard_matrix  # noqa: F401  (re-exported, as the reference module does)
 
@@ -78,7 +78,7 @@ class ResQForwardB200:
     """Decoder stack with packed weights resident on one GPU (one tensor-parallel rank)."""
 
     def __init__(self, cfg: LlamaConfig, device, ctx: Optional[tp.TPContext] = None, seed: int = 0,
-                 num_layers: Optional[int] = None, fused_reduce_rows: int = 0):
+                 num_layers: Optional[int] = None, fused_reduce_rows: int = 0, kv_quant: bool = False):
         self.cfg, self.device, self.ctx = cfg, torch.device(device), ctx or tp.TPContext()
         c, r, s = cfg, self.ctx.rank, self.ctx.size
         assert c.num_heads % s == 0 and c.num_kv_heads % s == 0 and c.intermediate_size % (s * 128) == 0
@@ -105,6 +105,11 @@ class ResQForwardB200:
         self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
         self.kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
         self.pos = 0
+        # keys go into the cache as NVFP4 (Hadamard over the head dimension, per-head rows), queries get the same
+        # rotation: the reference's QKRotationWrapper with k_had (promix/quantize/kv_quant.py:244-279)
+        self.kv_quant = kv_quant
+        if kv_quant and c.head_dim != 128:
+            raise ValueError("kv_quant needs head_dim = 128 (one Hadamard block per head)")
         # decode batches of up to `fused_reduce_rows` rows reduce over peer memory inside the RMSNorm-quant kernel
         self.peer = (tp.PeerReduce(fused_reduce_rows, c.hidden_size, self.device, self.ctx.group)
                      if fused_reduce_rows > 0 and self.ctx.size > 1 else None)
@@ -163,6 +168,9 @@ class ResQForwardB200:
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
         q, k = self._rope(q, k, cos_sin)
+        if self.kv_quant:
+            q = kv_cache.rotate_heads(q)
+            k = kv_cache.dequantize_heads(kv_cache.quantize_heads(k.contiguous()), k.shape)   # what the packed cache holds
         if static is None:
             if pos0 == 0:
                 self.kv[li] = (k, v)

@@ -17,6 +17,9 @@ from . import ops
 from .rotation import get_hadamard_matrix
 
 
+_H = {}
+
+
 def quantize_heads(x: torch.Tensor, k_hi: int = 0, hadamard: bool = True) -> ops.PackedMatrix:
     """x: bf16 [..., heads, head_dim] (keys after RoPE, or values) -> packed rows, one per (token, head).
     head_dim must be 128 for the rotation; k_hi is the MXFP8 channel count per head (the reference's
@@ -37,5 +40,8 @@ def dequantize_heads(p: ops.PackedMatrix, shape) -> torch.Tensor:
 def rotate_heads(q: torch.Tensor) -> torch.Tensor:
     """The same normalised Hadamard(128) on the head dimension of the queries (float32 product, one rounding:
     inference/quantize.py:447-448 in the reference)."""
-    h = get_hadamard_matrix(q.shape[-1]).to(q.device)
+    key = (q.shape[-1], q.device)
+    h = _H.get(key)
+    if h is None:                      # built once per device: no host-to-device copy inside a CUDA-graph capture
+        h = _H[key] = get_hadamard_matrix(q.shape[-1]).to(device=q.device, dtype=torch.float32)
     return (q.float() @ h).to(q.dtype)

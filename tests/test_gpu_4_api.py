@@ -149,3 +149,17 @@ def test_kv_cache_quantisation_per_head(k_hi):
     s_rot = torch.einsum("bthd,bshd->bhts", kv_cache.rotate_heads(q).float(), kv_cache.rotate_heads(k).float())
     assert rel_l2(s_rot.cpu().numpy(), s_ref.cpu().numpy()) < 1e-2     # the common rotation leaves the scores alone
     assert rel_l2(s_q.cpu().numpy(), s_ref.cpu().numpy()) < 0.35       # 4-bit keys with x20 outlier channels
+
+
+def test_decoder_with_quantised_key_cache():
+    """kv_quant: rotated queries against NVFP4 keys give logits close to the bf16-key run, eager and graph decode agree."""
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=128,
+                      vocab_size=500)
+    ids = torch.randint(0, 500, (2, 24), generator=torch.Generator().manual_seed(3)).cuda()
+    ref = ResQForwardB200(cfg, "cuda", seed=2).forward(ids)
+    model = ResQForwardB200(cfg, "cuda", seed=2, kv_quant=True)
+    got = model.forward(ids)
+    assert torch.isfinite(got).all() and rel_l2(got.cpu().numpy(), ref.cpu().numpy()) < 0.3
+    assert torch.equal(model.generate(ids, 4), model.generate(ids, 4, use_graph=False))
+    plq.check_device_status()
