@@ -254,31 +254,27 @@ def untile_sf(tiled: np.ndarray, rows: int, n: int) -> np.ndarray:
 # tests bound the distance from the torch composition (a bf16 ulp on a small share of elements).
 # ----------------------------------------------------------------------------------------
 def _sumsq_det(x: np.ndarray) -> np.ndarray:
-    """Row sum of squares, float32, in this order: inside each 128-block, four interleaved
-    partial sums p[q] (q = 0..3) over elements 32*j + 8*q + i, each the sum of two chains, one
-    over the even i and one over the odd i, both run sequentially (j outer 0..3, i inner), added
-    at the end; block sum = (p0 + p1) + (p2 + p3); blocks are combined eight at a time by
-    a balanced pairwise tree (missing blocks count as +0); the groups of eight are then added
-    left to right."""
+    """Row sum of squares, float32, in this order: the row is cut into chunks of 64 elements and every
+    chunk into two runs of 32; inside a run the even and the odd elements are accumulated in two
+    sequential chains, run sum = even + odd, chunk sum = run + run; chunks are combined 32 at a time
+    (2048 elements) by a balanced pairwise tree (missing chunks count as +0); the groups of 32 chunks
+    are then added left to right."""
     rows, k = x.shape
-    assert k % HAD_BLOCK == 0
-    sq = (x * x).astype(F32).reshape(rows, k // 128, 4, 4, 8)   # [.., blk, j, q, i]
-    pe = np.zeros((rows, k // 128, 4), dtype=F32)
-    po = np.zeros((rows, k // 128, 4), dtype=F32)
-    for j in range(4):
-        for i in range(0, 8, 2):
-            pe = pe + sq[:, :, j, :, i]
-            po = po + sq[:, :, j, :, i + 1]
-    p = pe + po
-    b = (p[..., 0] + p[..., 1]) + (p[..., 2] + p[..., 3])
-    nb = b.shape[1]
-    pad = -(-nb // 8) * 8
-    bb = np.zeros((rows, pad), dtype=F32)
-    bb[:, :nb] = b
-    g = bb.reshape(rows, pad // 8, 8)
-    g = g[..., 0::2] + g[..., 1::2]
-    g = g[..., 0::2] + g[..., 1::2]
-    g = g[..., 0] + g[..., 1]
+    assert k % 64 == 0
+    sq = (x * x).astype(F32).reshape(rows, k // 64, 2, 16, 2)   # [.., chunk, run, pair, even/odd]
+    acc = np.zeros((rows, k // 64, 2, 2), dtype=F32)
+    for i in range(16):
+        acc = acc + sq[:, :, :, i, :]
+    run = acc[..., 0] + acc[..., 1]
+    c = run[..., 0] + run[..., 1]
+    nc = c.shape[1]
+    pad = -(-nc // 32) * 32
+    cc = np.zeros((rows, pad), dtype=F32)
+    cc[:, :nc] = c
+    g = cc.reshape(rows, pad // 32, 32)
+    while g.shape[-1] > 1:
+        g = g[..., 0::2] + g[..., 1::2]
+    g = g[..., 0]
     tot = np.zeros(rows, dtype=F32)
     for w in range(g.shape[1]):
         tot = tot + g[:, w]
@@ -341,11 +337,36 @@ def add_bf16(residual: np.ndarray, x: np.ndarray) -> np.ndarray:
     return round_to_bf16(np.asarray(residual, dtype=F32) + np.asarray(x, dtype=F32))
 
 
+def exp_det(x: np.ndarray) -> np.ndarray:
+    """The float32 exponential of the SiLU prologue, operation by operation (every multiply and add is a
+    separately rounded IEEE float32 operation, no fused multiply-add); the CUDA kernel follows the same list:
+        x <- min(max(x, -100), 100);  n <- (x * log2(e) + 1.5 * 2^23) - 1.5 * 2^23
+        r <- (x - n * 0.693359375) - n * (-2.12194440e-4)
+        p <- Horner form of 1 + r + r^2/2 + ... + r^7/5040
+        exp <- (p * 2^floor(n/2)) * 2^(n - floor(n/2))"""
+    x = np.minimum(np.maximum(np.asarray(x, dtype=F32), F32(-100.0)), F32(100.0))
+    magic = F32(12582912.0)
+    n = (x * F32(1.44269502162933349609375) + magic) - magic
+    r = x - n * F32(0.693359375)
+    r = r - n * F32(-2.12194440e-4)
+    p = np.full_like(r, F32(1.98412701138295233249664306640625e-4))
+    for c in (1.388888922519981861114501953125e-3, 8.3333337679505348205566406250e-3,
+              4.16666679084300994873046875e-2, 0.1666666716337203979492187500, 0.5, 1.0, 1.0):
+        p = p * r + F32(c)
+    ni = n.astype(np.int32)
+    h = ni >> 1
+    s1 = ((h + 127).astype(np.uint32) << np.uint32(23)).view(F32)
+    s2 = ((ni - h + 127).astype(np.uint32) << np.uint32(23)).view(F32)
+    with np.errstate(over="ignore"):
+        return (p * s1) * s2
+
+
 def silu_mul_bf16(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
-    """F.silu(gate) * up on bf16 tensors: x / (1 + exp(-x)) in float32 rounded to bf16, then the product rounded
-    to bf16.  The float32 exponential of numpy and of the GPU may differ in the last place, which survives the
-    rounding to bf16 for about one element in 10^4: comparisons against this function allow for that."""
+    """F.silu(gate) * up on bf16 tensors: g / (1 + exp(-g)) in float32 rounded to bf16, then the product rounded
+    to bf16 (inference/forward_pass.py:266-269 in the reference), with the exponential of `exp_det`.  torch's own
+    float32 exp may differ from it in the last place, which survives the rounding to bf16 for about one element
+    in 10^4; the kernel matches this function bit for bit."""
     g = np.asarray(gate, dtype=F32)
     with np.errstate(over="ignore"):
-        s = round_to_bf16(g / (F32(1.0) + np.exp(-g, dtype=F32)))
+        s = round_to_bf16(g / (F32(1.0) + exp_det(-g)))
     return round_to_bf16(s * np.asarray(up, dtype=F32))

@@ -1,20 +1,39 @@
 // Quantise-and-pack kernels: [RMSNorm] -> [block-Hadamard 128] -> NVFP4 | MXFP8 codes + scales,
-// and the inverse (dequantise to bf16).  HBM-bound elementwise work, one CTA per row.
+// and the inverse (dequantise to bf16).  HBM-bound elementwise work.
 //
-// Thread mapping.  A row is cut into 128-element blocks (the Hadamard block).  Four
-// consecutive lanes (a "quad", q = lane & 3) own one block; lane q holds the 32 elements
-// e = 32*j + 8*q + i (j = 0..3, i = 0..7), i.e. four 16-byte loads, so every 32-byte sector
-// fetched from HBM is consumed whole.  In this mapping
-//   * butterfly strides 1,2,4 (bits of i) and 32,64 (bits of j) stay inside a lane,
-//     strides 8,16 (bits of q) are two shuffle rounds inside the quad;
-//   * an NVFP4 block (16 elements) is one j of lanes {0,1} or {2,3}: one shuffle for the max;
-//   * an MXFP8 block (32 elements) is one j of the whole quad: two shuffles;
-//   * the NVFP4/MXFP8 boundary (a multiple of 64) never cuts a j group.
+// Thread mapping.  A row is cut into 128-element blocks (the Hadamard block) and two consecutive
+// lanes own one block: lane l of a row loads the 64 contiguous elements [64 l, 64 l + 64) as two
+// runs of 32 (eight 16-byte loads), held as 2 x 16 float32 pairs.  A CTA works on `rows_per_cta`
+// rows at once.  In this mapping
+//   * butterfly strides 1..16 stay inside a run and stride 32 combines the two runs of a lane, so
+//     six of the seven stages need no other lane;
+//   * stride 64 pairs the two lanes of a block.  Each lane keeps one run and sends the other: the
+//     even lane ends up with the sums and differences of elements [0, 32) u [64, 96) of the block,
+//     the odd lane with [32, 64) u [96, 128): 32 shuffles per 64 elements instead of 64.  So that
+//     both lanes keep register run 0 and send run 1, the odd lane holds its runs swapped from the
+//     load on (run 0 = elements [96, 128)), which the stride-32 stage absorbs in the sign of one
+//     multiplier; the odd lane's differences come out negated and the sign returns in the final
+//     multiplication by +-1/sqrt(128) (negation is exact, so every element sees the same roundings
+//     as in the plain butterfly network);
+//   * after the rotation every lane holds two whole runs of 32 consecutive elements: the NVFP4
+//     blocks (16) and MXFP8 blocks (32) are lane-local - no shuffle for the block maxima, one
+//     scale computation per block, 16-byte code stores;
+//   * the NVFP4/MXFP8 boundary (a multiple of 64) never cuts a run.
 // Summation and butterfly order are fixed and documented in the CPU oracle
 // (`_sumsq_det`, `block_hadamard_det`), which these kernels match bit for bit.
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <utility>
+
 #include "plq_quant.cuh"
 
 namespace plq {
+
+#ifndef PLQ_PACK_TARGET_THREADS
+#define PLQ_PACK_TARGET_THREADS 128
+#endif
+constexpr int kPackTargetThreads = PLQ_PACK_TARGET_THREADS;   // CTA size the launcher aims for (whole rows)
 
 struct PackArgs {
   const uint4* x;        // bf16 [rows, k], row stride ldx8 * 8 elements
@@ -37,7 +56,124 @@ struct PackArgs {
   uint8_t* hi_sf;
   int sf_tiled;
   int lo_chunks, hi_chunks;  // chunks per 128-row group in the tiled layouts
+  int lanes;                 // threads per row: ceil(k / 64) rounded up to a whole warp
+  int rows_per_cta;
+  int stages;                // groups of rows in flight per CTA (1..3 shared-memory stages)
 };
+
+// Four 32-bit words of bf16 pairs -> four float32 pairs.
+__device__ __forceinline__ void unpack8(const uint4& w, float2* v) {
+  v[0] = make_float2(bf16lo_to_f32(w.x), bf16hi_to_f32(w.x));
+  v[1] = make_float2(bf16lo_to_f32(w.y), bf16hi_to_f32(w.y));
+  v[2] = make_float2(bf16lo_to_f32(w.z), bf16hi_to_f32(w.z));
+  v[3] = make_float2(bf16lo_to_f32(w.w), bf16hi_to_f32(w.w));
+}
+
+// Round a float32 pair to bf16 and widen it again.
+__device__ __forceinline__ float2 round_bf16_pair(const float2 y) {
+  const uint32_t b = f32x2_to_bf16x2(y.x, y.y);
+  return make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
+}
+
+// Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued) that starts at element `o` of row
+// `row` (o < k_lo), stores its 16 bytes of codes when `ok`, and returns its two scale bytes (block order).
+__device__ __forceinline__ uint32_t quantize_run_nvfp4(const PackArgs& a, const float2* v, int row, int o, bool ok) {
+  uint32_t sf2 = 0;
+  uint32_t words[4];
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    float m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      m0 = fmaxf(m0, fmaxf(fabsf(v[8 * b + i].x), fabsf(v[8 * b + i].y)));
+      m1 = fmaxf(m1, fmaxf(fabsf(v[8 * b + i + 1].x), fabsf(v[8 * b + i + 1].y)));
+    }
+    const uint32_t c = nvfp4_scale_code(fmaxf(m0, m1));
+    const float s = e4m3_code_to_f32(c);
+    const float r = __frcp_rn(s);
+    words[2 * b] = nvfp4_quantize8(v + 8 * b, s, r);
+    words[2 * b + 1] = nvfp4_quantize8(v + 8 * b + 4, s, r);
+    sf2 |= c << (8 * b);
+  }
+  if (ok)
+    *reinterpret_cast<uint4*>(a.lo_codes + (static_cast<size_t>(row) * a.k_lo + o) / 2) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  return sf2;
+}
+
+// The same for a run in the MXFP8 columns (o >= k_lo): 32 code bytes and one scale byte.
+__device__ __forceinline__ void quantize_run_mxfp8(const PackArgs& a, const float2* v, int row, int o) {
+  float m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    m0 = fmaxf(m0, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
+    m1 = fmaxf(m1, fmaxf(fabsf(v[i + 1].x), fabsf(v[i + 1].y)));
+  }
+  const uint32_t c = mxfp8_scale_code(fmaxf(m0, m1));
+  const float inv = __uint_as_float((254u - c) << 23);
+  const uint2 c0 = mxfp8_quantize8(v, inv), c1 = mxfp8_quantize8(v + 4, inv);
+  const uint2 c2 = mxfp8_quantize8(v + 8, inv), c3 = mxfp8_quantize8(v + 12, inv);
+  const int k_hi = a.k - a.k_lo, kh = o - a.k_lo;
+  uint4* dst = reinterpret_cast<uint4*>(a.hi_codes + static_cast<size_t>(row) * k_hi + kh);
+  dst[0] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+  dst[1] = make_uint4(c2.x, c2.y, c3.x, c3.y);
+  const int kb = kh >> 5;
+  const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.hi_chunks))
+                                : static_cast<size_t>(row) * (k_hi >> 5) + kb;
+  a.hi_sf[off] = static_cast<uint8_t>(c);
+}
+
+// ---- staging through shared memory -------------------------------------------------------
+// A warp works on one segment of a row: the 32 x 128 bytes its lanes own.  The segment travels global ->
+// shared memory as 16-byte asynchronous copies whose global addresses are consecutive across the warp
+// (coalesced), into a layout where lane `o` owns line o (128 bytes) with its eight 16-byte chunks XOR-swizzled
+// by (o & 7); each lane then reads its own line with conflict-free 16-byte loads.  Copies and reads of a
+// segment are warp-local, so only warp barriers order them.  Pieces outside the matrix are zero-filled.
+constexpr int kSegBytes = 4096;
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// waits until at most `pending` (0..2) of the most recently committed groups are still in flight
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  if (pending <= 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+  else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 2;" ::: "memory");
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// Starts the copy of one segment: `src` = first 16-byte piece of the segment in global memory, `npieces` = how
+// many of its 256 pieces exist (0 for a row outside the matrix).  Piece 32 j + lane goes to line 4 j + lane / 8,
+// chunk (lane & 7) ^ (line & 7): per lane two fixed offsets (even / odd j) plus 512 j.
+__device__ __forceinline__ void stage_segment(uint32_t seg_smem, const uint4* src, int npieces, int lane) {
+  const uint32_t q = static_cast<uint32_t>(lane) >> 3;
+  const uint32_t x = ((static_cast<uint32_t>(lane) & 7u) ^ q) << 4;
+  const uint32_t d_even = seg_smem + q * 128 + x, d_odd = seg_smem + q * 128 + (x ^ 64u);
+  const uint4* s = src + lane;
+  if (npieces == 256) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cp_async16(((j & 1) ? d_odd : d_even) + 512 * j, s + 32 * j);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool valid = 32 * j + lane < npieces;
+      cp_async16_zfill(((j & 1) ? d_odd : d_even) + 512 * j, valid ? s + 32 * j : src, valid);
+    }
+  }
+}
+
+// The lane's own eight pieces, register run 0 first; `xr` = ((lane & 7) ^ (4 if the runs are swapped)) << 4.
+__device__ __forceinline__ void read_line(const uint8_t* seg, int lane, uint32_t xr, uint4 (&w)[8]) {
+  const uint8_t* line = seg + lane * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) w[c] = *reinterpret_cast<const uint4*>(line + ((16u * c) ^ xr));
+}
 
 // PRO selects what is quantised: 0 = x; 1 = SiLU(x) * x2 (gate and up halves of the MLP, rounded to bf16 after
 // the activation and after the product like the two PyTorch ops they replace, inference/forward_pass.py:266
@@ -45,19 +181,55 @@ struct PackArgs {
 // 3 = like 2 with x = bf16(sum over the tensor-parallel ranks of their partial outputs), float32 sum in rank order,
 // read from the peers' memory: the all-reduce after a row-parallel linear, the residual add, the norm and the
 // quantiser of the next linear in one kernel.
+//
+// Persistent: a CTA of rows_per_cta x (lanes / 32) warps walks over groups of rows with a grid stride.  While a
+// group is computed from registers, the next group's segments are already on their way into shared memory.
+#ifdef PLQ_PACK_MAXNREG
+#define PLQ_PACK_BOUNDS __maxnreg__(PLQ_PACK_MAXNREG)
+#else
+#define PLQ_PACK_BOUNDS __launch_bounds__(512)
+#endif
 template <int PRO, bool NORM, bool HAD>
-__global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
+__global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
+  extern __shared__ __align__(1024) uint8_t pack_smem[];
   // Programmatic dependent launch on both sides.  A consumer launched with programmatic stream serialisation
   // (GEMM, decode GEMV) may set itself up and prefetch its weights while this kernel runs; it waits for this
   // grid's completion before reading the codes.  This kernel itself may be launched before its predecessor
   // has finished, and waits here before it reads anything.
   pdl_launch_dependents();
   pdl_wait();
-  const int row = blockIdx.x;
   const int tid = threadIdx.x;
-  const int q = tid & 3;
-  const int k0 = (tid >> 2) * 128;                  // first element of this quad's block
   const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int wpr = a.lanes >> 5;                     // warps (segments) per row
+  const int rl = warp / wpr;                        // which of the CTA's rows
+  const int seg = warp - rl * wpr;                  // which 2048-element segment of the row
+  const int l = 32 * seg + lane;                    // lane of the row: elements [64 l, 64 l + 64)
+  const int p = l & 1;
+  const int flip = HAD ? p : 0;                     // odd lanes of a rotated row hold their runs swapped
+  const int in0 = 64 * l + 32 * flip;               // first element of register run 0 / run 1 as loaded
+  const int in1 = 64 * l + 32 - 32 * flip;
+  const int k8 = a.k >> 3;
+  const uint32_t xr = static_cast<uint32_t>((lane & 7) ^ (4 * flip)) << 4;   // chunk swizzle of this lane's line, run 0 first
+  const int seg_pieces = min(max(k8 - 256 * seg, 0), 256);        // 16-byte pieces of this segment inside the row
+  constexpr bool kStageX = PRO != 3;                // prologue 3 reads x from the peers, straight into registers
+  constexpr bool kStageX2 = PRO != 0;
+  constexpr int kOperands = (kStageX ? 1 : 0) + (kStageX2 ? 1 : 0);
+  const int stage_bytes = kOperands * nwarps * kSegBytes;           // one group of rows, all staged operands
+  uint8_t* xs0 = pack_smem + warp * kSegBytes;                       // stage 0; stage s is s * stage_bytes further
+  uint8_t* x2s0 = pack_smem + ((kStageX ? nwarps : 0) + warp) * kSegBytes;
+  uint8_t* gs = pack_smem + a.stages * stage_bytes + seg * 2 * kSegBytes;   // gamma as float32: shared by the rows
+  const int ld2 = PRO == 1 ? a.ldx8 : k8;           // row stride of x2 in 16-byte units
+
+  auto stage_group = [&](int group, int slot) {
+    const int row = group * a.rows_per_cta + rl;
+    const int n = row < a.rows ? seg_pieces : 0;
+    const size_t r0 = static_cast<size_t>(row < a.rows ? row : 0);
+    if constexpr (kStageX) stage_segment(smem_u32(xs0 + slot * stage_bytes), a.x + r0 * a.ldx8 + 256 * seg, n, lane);
+    if constexpr (kStageX2) stage_segment(smem_u32(x2s0 + slot * stage_bytes), a.x2 + r0 * ld2 + 256 * seg, n, lane);
+  };
+
   if constexpr (PRO == 3) {
     // Cross-rank handshake.  Call number c = completed calls + 1.  This rank's partial output was written by
     // the preceding kernel of the stream; block 0 announces it by storing c into flags[rank] of every peer, and
@@ -82,234 +254,235 @@ __global__ void __launch_bounds__(1024) pack_kernel(const PackArgs a) {
     }
     __syncthreads();
   }
-  // v2[p] holds elements (2p, 2p+1) of the lane's 32, i.e. e = 8*j + i -> p = 4*j + i/2.  Arithmetic on
-  // pairs uses the packed float32x2 instructions of sm_100 (same IEEE rounding per element, half the issue slots).
-  float2 v2[16];
 
-  // ---- load: four 16-byte pieces per lane ---------------------------------------------
-  const uint4* xrow = a.x + static_cast<size_t>(row) * a.ldx8;
-  uint4 wsum[PRO == 3 ? 4 : 1];
-  if constexpr (PRO == 3) {
-    // x = bf16(sum over the ranks), float32 in rank order (every rank computes the same bits).  The peer loads
-    // of two of the lane's four pieces are all issued before any of them is used: two NVLink round trips per
-    // lane instead of one per rank and piece.
+  const int ngroups = (a.rows + a.rows_per_cta - 1) / a.rows_per_cta;
+  int group = blockIdx.x;
+  if constexpr (NORM) {
+    // The norm weights, widened to float32 once per CTA: lane `lane` of segment `seg` finds its 64 values, in its
+    // own register order, as sixteen 16-byte pieces at gs + (16 c + ...): piece c of all 32 lanes is contiguous.
+    if (rl == 0) {
 #pragma unroll
-    for (int jp = 0; jp < 4; jp += 2) {
-      uint4 t[2][8];
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int kk = k0 + 32 * (jp + jj) + 8 * q;
-        const size_t off = static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          t[jj][r] = make_uint4(0, 0, 0, 0);
-          if (r < a.world && kk < a.k)
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(t[jj][r].x), "=r"(t[jj][r].y), "=r"(t[jj][r].z), "=r"(t[jj][r].w)
-                         : "l"(a.peer_x[r] + off)
-                         : "memory");
-        }
+      for (int c = 0; c < 8; ++c) {
+        const int e = (c < 4 ? in0 : in1) + 8 * (c & 3);
+        const uint4 gq = e < a.k ? __ldg(a.gamma + (e >> 3)) : make_uint4(0, 0, 0, 0);
+        float2 g[4];
+        unpack8(gq, g);
+        float4* dst = reinterpret_cast<float4*>(gs) + (2 * c) * 32 + lane;
+        dst[0] = make_float4(g[0].x, g[0].y, g[1].x, g[1].y);
+        dst[32] = make_float4(g[2].x, g[2].y, g[3].x, g[3].y);
       }
+    }
+  }
+  const int stride = static_cast<int>(gridDim.x);
+  for (int s = 0; s < a.stages; ++s) {               // fill the ring: one committed copy group per stage
+    if (group + s * stride < ngroups) stage_group(group + s * stride, s);
+    cp_async_commit();
+  }
+  int iter = 0, slot = 0;
+
+  for (; group < ngroups; group += stride, ++iter) {
+    const int row = group * a.rows_per_cta + rl;
+    const bool row_ok = row < a.rows;
+    const bool ok0 = row_ok && in0 < a.k, ok1 = row_ok && in1 < a.k;
+    // v[16 r + 4 c + i] holds elements (8 c + 2 i, 8 c + 2 i + 1) of register run r.  Arithmetic on pairs uses the
+    // packed float32x2 instructions of sm_100 (same IEEE rounding per element, half the issue slots).
+    float2 v[32];
+
+    // ---- this group's pieces: shared memory -> registers; then the next group's copies start ----------
+    {
+      uint4 w[8], w2[8];
+      cp_async_wait_pending(a.stages - 1);          // the oldest group in flight is this one
+      if (NORM && iter == 0) __syncthreads();       // gamma was staged by the warps of the CTA's first row
+      else __syncwarp();
+      if constexpr (kStageX) read_line(xs0 + slot * stage_bytes, lane, xr, w);
+      if constexpr (kStageX2) read_line(x2s0 + slot * stage_bytes, lane, xr, w2);
+      __syncwarp();                                 // every lane has its pieces: the slot is free again
+      if (group + a.stages * stride < ngroups) stage_group(group + a.stages * stride, slot);
+      cp_async_commit();
+      if (++slot == a.stages) slot = 0;
+      if constexpr (PRO == 3) {
+        // x = bf16(sum over the ranks), float32 in rank order (every rank computes the same bits).  The peer loads
+        // of two of the lane's eight pieces are all issued before any of them is used.
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        for (int h = 0; h < 4; ++h) {
+          uint4 t[2][8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (r < a.world) {
-            const uint32_t tt[4] = {t[jj][r].x, t[jj][r].y, t[jj][r].z, t[jj][r].w};
+          for (int jj = 0; jj < 2; ++jj) {
+            const int piece = 2 * h + jj;
+            const int e = (piece < 4 ? in0 : in1) + 8 * (piece & 3);
+            const bool ok = piece < 4 ? ok0 : ok1;
+            const size_t off = static_cast<size_t>(row) * k8 + (e >> 3);
 #pragma unroll
-            for (int p = 0; p < 4; ++p)
-              acc[p] = __fadd2_rn(acc[p], make_float2(bf16lo_to_f32(tt[p]), bf16hi_to_f32(tt[p])));
+            for (int r = 0; r < 8; ++r) {
+              t[jj][r] = make_uint4(0, 0, 0, 0);
+              if (r < a.world && ok)
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(t[jj][r].x), "=r"(t[jj][r].y), "=r"(t[jj][r].z), "=r"(t[jj][r].w)
+                             : "l"(a.peer_x[r] + off)
+                             : "memory");
+            }
+          }
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (r < a.world) {
+                const uint32_t tt[4] = {t[jj][r].x, t[jj][r].y, t[jj][r].z, t[jj][r].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  acc[i] = __fadd2_rn(acc[i], make_float2(bf16lo_to_f32(tt[i]), bf16hi_to_f32(tt[i])));
+              }
+            }
+            w[2 * h + jj] = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
+                                       f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
           }
         }
-        wsum[jp + jj] = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
-                                   f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
       }
-    }
-  }
+      if constexpr (PRO == 0) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int kk = k0 + 32 * j + 8 * q;
-    uint4 w = make_uint4(0, 0, 0, 0);
-    if constexpr (PRO == 3) {
-      w = wsum[j];
-    } else {
-      if (kk < a.k) w = __ldg(xrow + (kk >> 3));
-    }
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    if constexpr (PRO == 0) {
+        for (int c = 0; c < 8; ++c) unpack8(w[c], v + 4 * c);
+      } else if constexpr (PRO == 1) {
 #pragma unroll
-      for (int p = 0; p < 4; ++p) v2[4 * j + p] = make_float2(bf16lo_to_f32(ww[p]), bf16hi_to_f32(ww[p]));
-    } else if constexpr (PRO == 1) {
-      uint4 u = make_uint4(0, 0, 0, 0);
-      if (kk < a.k) u = __ldg(a.x2 + static_cast<size_t>(row) * a.ldx8 + (kk >> 3));
-      const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+          const uint32_t uu[4] = {w2[c].x, w2[c].y, w2[c].z, w2[c].w};
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const float g0 = bf16lo_to_f32(ww[p]), g1 = bf16hi_to_f32(ww[p]);
-        const uint32_t t = f32x2_to_bf16x2(g0 / (1.0f + expf(-g0)), g1 / (1.0f + expf(-g1)));   // SiLU, to bf16
-        const float2 prod = __fmul2_rn(make_float2(bf16lo_to_f32(t), bf16hi_to_f32(t)),
-                                       make_float2(bf16lo_to_f32(uu[p]), bf16hi_to_f32(uu[p])));
-        const uint32_t b = f32x2_to_bf16x2(prod.x, prod.y);                                       // product, to bf16
-        v2[4 * j + p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
-      }
-    } else {
-      uint4 r = make_uint4(0, 0, 0, 0);
-      if (kk < a.k) r = __ldg(a.x2 + static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3));
-      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-      uint32_t hh[4];
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t t = f32x2_to_bf16x2(silu_det(bf16lo_to_f32(ww[i])), silu_det(bf16hi_to_f32(ww[i])));   // SiLU, to bf16
+            const float2 prod = __fmul2_rn(make_float2(bf16lo_to_f32(t), bf16hi_to_f32(t)),
+                                           make_float2(bf16lo_to_f32(uu[i]), bf16hi_to_f32(uu[i])));
+            v[4 * c + i] = round_bf16_pair(prod);                                                                  // product, to bf16
+          }
+        }
+      } else {
+        uint4* hrow = a.h_out + static_cast<size_t>(row) * k8;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const float2 sum = __fadd2_rn(make_float2(bf16lo_to_f32(rr[p]), bf16hi_to_f32(rr[p])),
-                                      make_float2(bf16lo_to_f32(ww[p]), bf16hi_to_f32(ww[p])));
-        hh[p] = f32x2_to_bf16x2(sum.x, sum.y);
-        v2[4 * j + p] = make_float2(bf16lo_to_f32(hh[p]), bf16hi_to_f32(hh[p]));
-      }
-      if (kk < a.k) a.h_out[static_cast<size_t>(row) * (a.k >> 3) + (kk >> 3)] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
-    }
-  }
-
-  // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
-  if constexpr (NORM) {
-    __shared__ float warp_sums[32];
-    uint4 gpre[4];                                      // the norm weights: requested now, needed after the row sum
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+          const uint32_t rr[4] = {w2[c].x, w2[c].y, w2[c].z, w2[c].w};
+          uint32_t hh[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int kk = k0 + 32 * j + 8 * q;
-      gpre[j] = make_uint4(0, 0, 0, 0);
-      if (kk < a.k) gpre[j] = __ldg(a.gamma + (kk >> 3));
-    }
-    float2 s2 = make_float2(0.0f, 0.0f);               // even and odd elements accumulate separately
-#pragma unroll
-    for (int p = 0; p < 16; ++p) s2 = __ffma2_rn(v2[p], v2[p], s2);   // v*v is exact for bf16 inputs
-    float s = __fadd_rn(s2.x, s2.y);
-    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 2);              // (p0+p1)+(p2+p3): block sum
-    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 8);
-    s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 16);             // eight blocks, pairwise tree
-    if (lane == 0) warp_sums[tid >> 5] = s;
-    __syncthreads();
-    float tot = 0.0f;
-    const int nwarps = blockDim.x >> 5;
-    for (int w = 0; w < nwarps; ++w) tot = tot + warp_sums[w];  // left to right
-    const float var = __fdiv_rn(tot, static_cast<float>(a.k));
-    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
-    const float2 r2 = make_float2(r, r);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t gw[4] = {gpre[j].x, gpre[j].y, gpre[j].z, gpre[j].w};
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const float2 y = __fmul2_rn(make_float2(bf16lo_to_f32(gw[p]), bf16hi_to_f32(gw[p])), __fmul2_rn(v2[4 * j + p], r2));
-        const uint32_t b = f32x2_to_bf16x2(y.x, y.y);
-        v2[4 * j + p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
-      }
-    }
-  }
-
-  // ---- block-Hadamard(128): strides 1,2,4 | 8,16 (shuffles) | 32,64, then * 1/sqrt(128) ----
-  if constexpr (HAD) {
-    const float2 neg1 = make_float2(-1.0f, -1.0f);
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {                       // stride 1: inside a pair
-      const float x0 = v2[p].x, x1 = v2[p].y;
-      v2[p] = make_float2(__fadd_rn(x0, x1), __fsub_rn(x0, x1));
-    }
-#pragma unroll
-    for (int h = 1; h < 4; h <<= 1) {                    // strides 2, 4: pairs p, p + h
-#pragma unroll
-      for (int p = 0; p < 16; ++p) {
-        if ((p & h) == 0) {
-          const float2 x0 = v2[p], x1 = v2[p + h];
-          v2[p] = __fadd2_rn(x0, x1);
-          v2[p + h] = __ffma2_rn(x1, neg1, x0);          // x0 - x1: exact product, one rounding
+          for (int i = 0; i < 4; ++i) {
+            const float2 sum = __fadd2_rn(make_float2(bf16lo_to_f32(rr[i]), bf16hi_to_f32(rr[i])),
+                                          make_float2(bf16lo_to_f32(ww[i]), bf16hi_to_f32(ww[i])));
+            hh[i] = f32x2_to_bf16x2(sum.x, sum.y);
+            v[4 * c + i] = make_float2(bf16lo_to_f32(hh[i]), bf16hi_to_f32(hh[i]));
+          }
+          if (c < 4 ? ok0 : ok1) hrow[((c < 4 ? in0 : in1) >> 3) + (c & 3)] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
         }
       }
     }
+
+    // ---- RMSNorm (inference/forward_pass.py:33-39 in the reference) ------------------------
+    if constexpr (NORM) {
+      __shared__ float warp_sums[2][16];
+      float2 s0 = make_float2(0.0f, 0.0f), s1 = make_float2(0.0f, 0.0f);   // per run: even and odd elements apart
 #pragma unroll
-    for (int m = 1; m <= 2; m <<= 1) {                   // strides 8, 16: across the quad
-      const float sg = (q & m) ? -1.0f : 1.0f;           // upper lane of the pair computes partner - own
-      const float2 sgn = make_float2(sg, sg);
+      for (int i = 0; i < 16; ++i) {
+        s0 = __ffma2_rn(v[i], v[i], s0);                  // v*v is exact for bf16 inputs
+        s1 = __ffma2_rn(v[16 + i], v[16 + i], s1);
+      }
+      float s = __fadd_rn(__fadd_rn(s0.x, s0.y), __fadd_rn(s1.x, s1.y));   // symmetric in the two runs
+      s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+      s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+      s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+      s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 8);
+      s = s + __shfl_xor_sync(0xFFFFFFFFu, s, 16);             // 32 lanes = 2048 elements, pairwise tree
+      float* sums = warp_sums[iter & 1];                       // two sets: one barrier per group is enough
+      if (lane == 0) sums[warp] = s;
+      asm volatile("bar.sync %0, %1;" ::"r"(rl + 1), "r"(a.lanes) : "memory");   // the warps of this row only
+      float tot = 0.0f;
+      for (int w = 0; w < wpr; ++w) tot = tot + sums[rl * wpr + w];   // left to right
+      const float var = __fdiv_rn(tot, static_cast<float>(a.k));
+      const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+      const float2 r2 = make_float2(r, r);
+      const float4* gl = reinterpret_cast<const float4*>(gs) + lane;
 #pragma unroll
-      for (int p = 0; p < 16; ++p) {
-        float2 o;
-        o.x = __shfl_xor_sync(0xFFFFFFFFu, v2[p].x, m);
-        o.y = __shfl_xor_sync(0xFFFFFFFFu, v2[p].y, m);
-        v2[p] = __ffma2_rn(sgn, v2[p], o);               // own + other / other - own
+      for (int c = 0; c < 16; ++c) {
+        const float4 g = gl[32 * c];
+        v[2 * c] = round_bf16_pair(__fmul2_rn(make_float2(g.x, g.y), __fmul2_rn(v[2 * c], r2)));
+        v[2 * c + 1] = round_bf16_pair(__fmul2_rn(make_float2(g.z, g.w), __fmul2_rn(v[2 * c + 1], r2)));
       }
     }
+
+    // ---- block-Hadamard(128): strides 1..16 inside a run, 32 across the runs, 64 across the lane pair ----
+    if constexpr (HAD) {
+      const float2 neg1 = make_float2(-1.0f, -1.0f);
 #pragma unroll
-    for (int h = 4; h < 16; h <<= 1) {                   // strides 32, 64: pairs p, p + h
+      for (int i = 0; i < 32; ++i) {                       // stride 1: inside a pair
+        const float x0 = v[i].x, x1 = v[i].y;
+        v[i] = make_float2(__fadd_rn(x0, x1), __fsub_rn(x0, x1));
+      }
 #pragma unroll
-      for (int p = 0; p < 16; ++p) {
-        if ((p & h) == 0) {
-          const float2 x0 = v2[p], x1 = v2[p + h];
-          v2[p] = __fadd2_rn(x0, x1);
-          v2[p + h] = __ffma2_rn(x1, neg1, x0);
+      for (int h = 1; h < 16; h <<= 1) {                   // strides 2, 4, 8, 16: pairs i, i + h of one run
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if ((i & h) == 0) {
+            const float2 x0 = v[i], x1 = v[i + h];
+            v[i] = __fadd2_rn(x0, x1);
+            v[i + h] = __ffma2_rn(x1, neg1, x0);           // x0 - x1: exact product, one rounding
+          }
+        }
+      }
+      {                                                    // stride 32: run 0 with run 1
+        // even lane: run 0 = lower elements: (P, Q) -> (P + Q, P - Q); odd lane: run 0 = upper: (P, Q) -> (Q - P, Q + P)
+        const float sg = p ? -1.0f : 1.0f;
+        const float2 sp = make_float2(sg, sg), sn = make_float2(-sg, -sg);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 P = v[i], Q = v[16 + i];
+          v[i] = __ffma2_rn(P, sp, Q);
+          v[16 + i] = __ffma2_rn(Q, sn, P);
+        }
+      }
+      {                                                    // stride 64: keep run 0, trade run 1 with the other lane
+        const float c = 0.088388347648318441f;             // 1/sqrt(128), then to bf16
+        const float2 c0 = make_float2(c, c), c1 = make_float2(p ? -c : c, p ? -c : c);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float2 o;
+          o.x = __shfl_xor_sync(0xFFFFFFFFu, v[16 + i].x, 1);
+          o.y = __shfl_xor_sync(0xFFFFFFFFu, v[16 + i].y, 1);
+          const float2 k = v[i];
+          const float2 sum = __fadd2_rn(k, o);             // elements [32 p, 32 p + 32) of the block
+          const float2 dif = __ffma2_rn(o, neg1, k);       // elements [64 + 32 p, ...): negated in the odd lane
+          v[i] = round_bf16_pair(__fmul2_rn(sum, c0));
+          v[16 + i] = round_bf16_pair(__fmul2_rn(dif, c1));
         }
       }
     }
-    const float2 scale = make_float2(0.088388347648318441f, 0.088388347648318441f);
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {
-      const float2 y = __fmul2_rn(v2[p], scale);
-      const uint32_t b = f32x2_to_bf16x2(y.x, y.y);
-      v2[p] = make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
-    }
-  }
 
-  // ---- quantise, 32 elements (one j group of the quad) at a time ---------------------------
-  uint32_t lo_sf_bytes = 0;                           // this lane pair's scale byte for j = 0..3
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int kg = k0 + 32 * j;                       // first element of the quad's j group
-    float x8[8];
-    float m = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      x8[2 * i] = v2[4 * j + i].x;
-      x8[2 * i + 1] = v2[4 * j + i].y;
-      m = fmaxf(m, fmaxf(fabsf(x8[2 * i]), fabsf(x8[2 * i + 1])));
+    // ---- quantise: two runs of 32 consecutive elements per lane -------------------------------
+    // first element of the run now in v[0..15] / v[16..31]
+    const int o0 = HAD ? 128 * (l >> 1) + 32 * p : 64 * l;
+    const int o1 = HAD ? o0 + 64 : o0 + 32;
+    uint32_t sf;
+    const bool hi0 = o0 >= a.k_lo && o0 < a.k, hi1 = o1 >= a.k_lo && o1 < a.k;
+    if (!__any_sync(0xFFFFFFFFu, hi0 || hi1)) {     // the usual case: the whole warp is in the NVFP4 columns
+      sf = quantize_run_nvfp4(a, v, row, o0, row_ok && o0 < a.k_lo);
+      sf |= quantize_run_nvfp4(a, v + 16, row, o1, row_ok && o1 < a.k_lo) << 16;
+    } else {                                         // a warp that holds MXFP8 columns
+      sf = 0;
+      if (o0 < a.k_lo) sf = quantize_run_nvfp4(a, v, row, o0, row_ok);
+      else if (hi0 && row_ok) quantize_run_mxfp8(a, v, row, o0);
+      if (o1 < a.k_lo) sf |= quantize_run_nvfp4(a, v + 16, row, o1, row_ok) << 16;
+      else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, row, o1);
     }
-    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
-    const float m32 = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-    if (kg >= a.k) continue;
-    if (kg < a.k_lo) {
-      const uint32_t c = nvfp4_scale_code(m);
-      const float s = e4m3_code_to_f32(c);
-      const uint32_t codes = nvfp4_quantize8(x8, s, __frcp_rn(s));
-      *reinterpret_cast<uint32_t*>(a.lo_codes + (static_cast<size_t>(row) * a.k_lo + kg + 8 * q) / 2) = codes;
-      lo_sf_bytes |= c << (8 * j);
-    } else {
-      const uint32_t c = mxfp8_scale_code(m32);
-      const uint2 codes = mxfp8_quantize8(x8, __uint_as_float((254u - c) << 23));
-      const int kh = kg - a.k_lo;
-      *reinterpret_cast<uint2*>(a.hi_codes + static_cast<size_t>(row) * (a.k - a.k_lo) + kh + 8 * q) = codes;
-      if (q == 0) {
-        const int kb = kh >> 5;
-        const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.hi_chunks))
-                                      : static_cast<size_t>(row) * ((a.k - a.k_lo) >> 5) + kb;
-        a.hi_sf[off] = static_cast<uint8_t>(c);
-      }
+    // NVFP4 scale bytes, one 32-bit word per 64 elements.  Plain rows: the lane's own four bytes.  Rotated rows:
+    // the even lane has bytes 0,1 of both words of its block and the odd lane bytes 2,3: one exchange, one word each.
+    if constexpr (HAD) {
+      const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, sf, 1);
+      sf = p ? __byte_perm(sf, other, 0x3276) : __byte_perm(sf, other, 0x5410);
+    }
+    if (row_ok && 64 * l < a.k_lo) {
+      const int kb = 4 * l;
+      const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.lo_chunks))
+                                    : static_cast<size_t>(row) * (a.k_lo >> 4) + kb;
+      *reinterpret_cast<uint32_t*>(a.lo_sf + off) = sf;
     }
   }
-  // NVFP4 scales: lanes 0/1 of the quad hold blocks 0,2,4,6 (one byte per j), lanes 2/3 hold
-  // blocks 1,3,5,7.  Lane 0 interleaves them into two 4-byte words (64 elements each).
-  const uint32_t odd = __shfl_xor_sync(0xFFFFFFFFu, lo_sf_bytes, 2);
-  if (q == 0) {
-    const uint32_t w0 = __byte_perm(lo_sf_bytes, odd, 0x5140);   // blocks 0,1,2,3
-    const uint32_t w1 = __byte_perm(lo_sf_bytes, odd, 0x7362);   // blocks 4,5,6,7
-    const int kb = k0 >> 4;                                      // first 16-block index of this quad
-    if (a.sf_tiled) {
-      if (k0 < a.k_lo) *reinterpret_cast<uint32_t*>(a.lo_sf + sf_tiled_offset(row, kb, a.lo_chunks)) = w0;
-      if (k0 + 64 < a.k_lo) *reinterpret_cast<uint32_t*>(a.lo_sf + sf_tiled_offset(row, kb + 4, a.lo_chunks)) = w1;
-    } else {
-      uint8_t* p = a.lo_sf + static_cast<size_t>(row) * (a.k_lo >> 4) + kb;
-      if (k0 < a.k_lo) *reinterpret_cast<uint32_t*>(p) = w0;
-      if (k0 + 64 < a.k_lo) *reinterpret_cast<uint32_t*>(p + 4) = w1;
-    }
-  }
+  cp_async_wait_all();
   if constexpr (PRO == 3) {
     // the last block to finish closes the call: the counter the next call's handshake is derived from
     __syncthreads();
@@ -371,6 +544,34 @@ __global__ void unpack_kernel(const UnpackArgs a) {
   o.x = f32x2_to_bf16x2(f[0], f[1]); o.y = f32x2_to_bf16x2(f[2], f[3]);
   o.z = f32x2_to_bf16x2(f[4], f[5]); o.w = f32x2_to_bf16x2(f[6], f[7]);
   a.y[idx] = o;
+}
+
+// CTAs of `kernel` that fit one SM with this block size and dynamic shared memory, looked up once per
+// (device, kernel, configuration); the first use on a device also raises the kernel's shared-memory limit.
+static int resident_ctas(const void* kernel, int threads, int smem, int* per_sm) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, const void*, int, int>, int> cache;
+  static std::map<std::pair<int, const void*>, bool> raised;
+  int dev = 0;
+  PLQ_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (!raised[{dev, kernel}]) {
+    cudaFuncAttributes fa;
+    PLQ_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
+    PLQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      227 * 1024 - static_cast<int>(fa.sharedSizeBytes)));
+    raised[{dev, kernel}] = true;
+  }
+  const auto key = std::make_tuple(dev, kernel, threads, smem);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    int n = 0;
+    PLQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, static_cast<size_t>(smem)));
+    if (n < 1) return PLQ_ERR_LIMIT;
+    it = cache.emplace(key, n).first;
+  }
+  *per_sm = it->second;
+  return PLQ_OK;
 }
 
 static int check_pack_args(const void* x, int64_t rows, int64_t k, int64_t k_hi, int hadamard, bool norm,
@@ -441,35 +642,59 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.sf_tiled = sf_layout == PLQ_SF_TILED;
   a.lo_chunks = static_cast<int>(((k - k_hi) / 16 + 3) / 4);
   a.hi_chunks = static_cast<int>((k_hi / 32 + 3) / 4);
-  const int blocks128 = static_cast<int>((k + 127) / 128);
-  const int threads = ((blocks128 * 4 + 31) / 32) * 32;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(rows), 1, 1);
-  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  auto launch = [&](void (*kernel)(const PackArgs)) { return cudaLaunchKernelEx(&cfg, kernel, a); };
+  // threads per row: one per 64 elements, whole warps; rows per CTA: as many as fit the target CTA size, fewer
+  // when the groups of rows would not cover the GPU a few times over (decode batches)
+  const int lanes = ((static_cast<int>((k + 63) / 64) + 31) / 32) * 32;
+  int rpc = kPackTargetThreads / lanes;
+  if (rpc < 1) rpc = 1;
+  if (rpc > 8) rpc = 8;                               // one named barrier per row of the CTA
+  while (rpc > 1 && (rows + rpc - 1) / rpc < 4 * static_cast<int64_t>(sm_count())) rpc >>= 1;
+  a.lanes = lanes;
+  a.rows_per_cta = rpc;
+  const int threads = lanes * rpc;
+  // shared memory: `stages` groups of rows in flight (each: the staged operands of all warps) + gamma.  Kernels
+  // that do little arithmetic per byte (no norm) need more bytes in flight to cover the HBM latency.
+  const int stage_bytes = ((pro != 3) + (pro != 0)) * (threads / 32) * kSegBytes;
+  const int gamma_bytes = norm ? (lanes / 32) * 2 * kSegBytes : 0;      // float32 copy of the norm weights
+  int stages = (pro == 0 && !norm) ? 3 : 2;
+  while (stages > 1 && 4 * (stages * stage_bytes + gamma_bytes) > 216 * 1024) --stages;   // keep four CTAs per SM
+  a.stages = stages;
+  const int smem = stages * stage_bytes + gamma_bytes;
+  const int64_t groups = (rows + rpc - 1) / rpc;
+  auto launch = [&](void (*kernel)(const PackArgs)) -> int {
+    int per_sm = 0;
+    const int st = resident_ctas(reinterpret_cast<const void*>(kernel), threads, smem, &per_sm);
+    if (st != PLQ_OK) return st;
+    const int64_t resident = static_cast<int64_t>(per_sm) * sm_count();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(groups < resident ? groups : resident), 1, 1);   // persistent: grid stride over the groups
+    cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PLQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, a));
+    return PLQ_OK;
+  };
+  int st2 = PLQ_OK;
   if (pro == 1) {                      // SiLU(gate) * up: no norm in front of the down projection
     if (norm) return PLQ_ERR_SHAPE;
-    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<1, false, true>));
-    else PLQ_CUDA_TRY(launch(pack_kernel<1, false, false>));
+    st2 = hadamard ? launch(pack_kernel<1, false, true>) : launch(pack_kernel<1, false, false>);
   } else if (pro == 3) {               // all-reduce over peer memory, residual add, then RMSNorm
     if (!norm) return PLQ_ERR_NULL;
-    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<3, true, true>));
-    else PLQ_CUDA_TRY(launch(pack_kernel<3, true, false>));
+    st2 = hadamard ? launch(pack_kernel<3, true, true>) : launch(pack_kernel<3, true, false>);
   } else if (pro == 2) {               // residual add, then RMSNorm
     if (!norm) return PLQ_ERR_NULL;
-    if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<2, true, true>));
-    else PLQ_CUDA_TRY(launch(pack_kernel<2, true, false>));
-  } else if (norm && hadamard) PLQ_CUDA_TRY(launch(pack_kernel<0, true, true>));
-  else if (norm) PLQ_CUDA_TRY(launch(pack_kernel<0, true, false>));
-  else if (hadamard) PLQ_CUDA_TRY(launch(pack_kernel<0, false, true>));
-  else PLQ_CUDA_TRY(launch(pack_kernel<0, false, false>));
-  return PLQ_OK;
+    st2 = hadamard ? launch(pack_kernel<2, true, true>) : launch(pack_kernel<2, true, false>);
+  } else if (norm) {
+    st2 = hadamard ? launch(pack_kernel<0, true, true>) : launch(pack_kernel<0, true, false>);
+  } else {
+    st2 = hadamard ? launch(pack_kernel<0, false, true>) : launch(pack_kernel<0, false, false>);
+  }
+  return st2;
 }
 
 }  // namespace plq

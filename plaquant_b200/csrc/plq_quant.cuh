@@ -55,18 +55,15 @@ __device__ __forceinline__ uint32_t nvfp4_scale_code(float bmax) {
   return min(c, 0x7Eu);              // saturate at 448, never the NaN code
 }
 
-// Eight float32 (bf16-valued) -> eight E2M1 codes, element 0 in bits [0,4).
-__device__ __forceinline__ uint32_t nvfp4_quantize8(const float (&x)[8], float s, float r) {
-  float q[8];
+// Eight float32 (bf16-valued, four pairs) -> eight E2M1 codes, element 0 in bits [0,4).
+__device__ __forceinline__ uint32_t nvfp4_quantize8(const float2* x, float s, float r) {
+  float2 q[4];
   const float2 r2 = make_float2(r, r), ns2 = make_float2(-s, -s);
 #pragma unroll
-  for (int i = 0; i < 8; i += 2) {
-    const float2 xv = make_float2(x[i], x[i + 1]);
-    const float2 q0 = __fmul2_rn(xv, r2);
-    const float2 e = __ffma2_rn(ns2, q0, xv);
-    const float2 q1 = __ffma2_rn(e, r2, q0);
-    q[i] = q1.x;
-    q[i + 1] = q1.y;
+  for (int i = 0; i < 4; ++i) {
+    const float2 q0 = __fmul2_rn(x[i], r2);
+    const float2 e = __ffma2_rn(ns2, q0, x[i]);
+    q[i] = __ffma2_rn(e, r2, q0);
   }
   uint32_t out;
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
@@ -76,7 +73,7 @@ __device__ __forceinline__ uint32_t nvfp4_quantize8(const float (&x)[8], float s
       "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
       "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
       : "=r"(out)
-      : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+      : "f"(q[0].x), "f"(q[0].y), "f"(q[1].x), "f"(q[1].y), "f"(q[2].x), "f"(q[2].y), "f"(q[3].x), "f"(q[3].y));
   // No sign fix-up is needed here: the quotient is zero only for x = +-0, and for x = -0 the two
   // refinement FMAs already turn it into +0 (e = (-s)(-0) + (-0) = +0, q = (+0) r + (-0) = +0), which is
   // what the reference's sign(x/s) * |q| gives; a negative x that merely rounds to zero keeps its sign.
@@ -94,31 +91,63 @@ __device__ __forceinline__ uint32_t mxfp8_scale_code(float bmax) {
   return static_cast<uint32_t>(max(code, 1));          // floor 2^-126
 }
 
-// Eight float32 -> eight E4M3 bytes (element 0 in the low byte of .x); inv = 2^-e.
-__device__ __forceinline__ uint2 mxfp8_quantize8(const float (&x)[8], float inv) {
-  float q[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = x[i] * inv;
+// Eight float32 (four pairs) -> eight E4M3 bytes (element 0 in the low byte of .x); inv = 2^-e.
+// The reference multiplies the rounded magnitude by sign(x / s), so a quotient that is exactly zero must lose
+// its sign while a negative one that merely rounds to zero keeps it: fl(x * inv) + (+0) does that (-0 + +0 = +0,
+// every other value unchanged); x * inv is exact apart from underflow, where it rounds like the reference's x / s
+// (so the product is rounded on its own, not fused with the addition).
+__device__ __forceinline__ uint2 mxfp8_quantize8(const float2* x, float inv) {
   uint16_t h[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[i]) : "f"(q[2 * i + 1]), "f"(q[2 * i]));
+  for (int i = 0; i < 4; ++i) {
+    // scalar _rn intrinsics: never contracted into one fused multiply-add (which would round the exact tiny
+    // product straight to -0 and keep the sign)
+    const float q0 = __fadd_rn(__fmul_rn(x[i].x, inv), 0.0f), q1 = __fadd_rn(__fmul_rn(x[i].y, inv), 0.0f);
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[i]) : "f"(q1), "f"(q0));
+  }
   uint2 out;
   out.x = static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16);
   out.y = static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16);
-  uint32_t k0 = 0, k1 = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    k0 |= (q[i] != 0.0f ? 0xFFu : 0x7Fu) << (8 * i);
-    k1 |= (q[4 + i] != 0.0f ? 0xFFu : 0x7Fu) << (8 * i);
-  }
-  out.x &= k0;
-  out.y &= k1;
   return out;
 }
 
 // 2^(code-127) as float32 for an E8M0 byte in [1, 254].
 __device__ __forceinline__ float e8m0_to_f32(uint32_t code) { return __uint_as_float(code << 23); }
+
+// ---- SiLU with a written-down float32 exponential -------------------------------------------
+// exp(x) for the SiLU prologue, defined operation by operation so that the CPU checker can restate it
+// bit for bit (a library expf is only specified to a few units in the last place): every multiply and
+// add below is a separately rounded IEEE float32 operation (no fused multiply-add), in this order:
+//   x  <- min(max(x, -100), 100)
+//   n  <- (x * log2(e) + 1.5 * 2^23) - 1.5 * 2^23           (nearest integer, ties to even)
+//   r  <- (x - n * 0.693359375) - n * (-2.12194440e-4)       (Cody-Waite split of ln 2)
+//   p  <- 1 + r (1 + r (1/2 + r (1/6 + r (1/24 + r (1/120 + r (1/720 + r / 5040))))))   (Horner)
+//   exp <- (p * 2^floor(n/2)) * 2^(n - floor(n/2))           (two exact scalings; overflows to +inf)
+// |r| <= 0.3466, so the truncated series is within 6e-9 of e^r; the result is within ~2 ulp of exp(x).
+__device__ __forceinline__ float exp_det(float x) {
+  x = fminf(fmaxf(x, -100.0f), 100.0f);
+  const float magic = 12582912.0f;
+  const float n = __fsub_rn(__fadd_rn(__fmul_rn(x, 1.44269502162933349609375f), magic), magic);
+  float r = __fsub_rn(x, __fmul_rn(n, 0.693359375f));
+  r = __fsub_rn(r, __fmul_rn(n, -2.12194440e-4f));
+  float p = 1.98412701138295233249664306640625e-4f;                       // 1/5040
+  p = __fadd_rn(__fmul_rn(p, r), 1.388888922519981861114501953125e-3f);    // 1/720
+  p = __fadd_rn(__fmul_rn(p, r), 8.3333337679505348205566406250e-3f);      // 1/120
+  p = __fadd_rn(__fmul_rn(p, r), 4.16666679084300994873046875e-2f);        // 1/24
+  p = __fadd_rn(__fmul_rn(p, r), 0.1666666716337203979492187500f);         // 1/6
+  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  const int ni = __float2int_rn(n);
+  const int h = ni >> 1;
+  const float s1 = __uint_as_float(static_cast<uint32_t>(h + 127) << 23);
+  const float s2 = __uint_as_float(static_cast<uint32_t>(ni - h + 127) << 23);
+  return __fmul_rn(__fmul_rn(p, s1), s2);
+}
+
+// SiLU(g) = g / (1 + exp(-g)), float32, IEEE division (torch.nn.functional.silu on a bf16 tensor computes in
+// float32 and rounds once; the caller does that rounding).
+__device__ __forceinline__ float silu_det(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, exp_det(-g))); }
 
 #endif  // __CUDACC__
 }  // namespace plq
