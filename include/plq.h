@@ -202,7 +202,9 @@ PLQ_API int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void* a_
  * that loads the library, until the process exits), which limits this entry point to
  * n <= 32768 output features: larger n returns PLQ_ERR_LIMIT.  The call allocates and frees
  * nothing.  The first call on each device looks up the array's device address and zeroes its
- * ticket area; make that first call before any stream capture.  All calls on a device share the
+ * ticket area (after all argument checks have passed); make that first call before any stream
+ * capture.  Host threads may make it concurrently: they resolve the same address, which is
+ * published atomically.  All calls on a device share the
  * one array (it keeps the previous call's partial sums, which the next call overwrites before
  * reading): calls that overlap on the GPU, e.g. on two streams, race and must be serialised by
  * the caller.

@@ -23,6 +23,7 @@
 //   * With more than one K slice, partial sums go to a float32 scratch buffer; the warp that
 //     delivers the last slice of a tile (an atomic ticket per tile) adds them in slice order, so
 //     the result does not depend on timing, writes y and resets the ticket.
+#include <atomic>
 #include "plq_quant.cuh"
 
 namespace plq {
@@ -338,6 +339,22 @@ static int launch_gemv(const GemvArgs& a, int grid, size_t smem, cudaStream_t st
   return PLQ_OK;
 }
 
+// Argument and device checks shared by the two GEMV entry points; nothing is launched or touched before they pass.
+static int check_gemv_args(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes, const void* a_hi_sf,
+                           const void* b_lo_codes, const void* b_lo_sf, const void* b_hi_codes, const void* b_hi_sf,
+                           int64_t m, int64_t n, int64_t k_lo, int64_t k_hi, const void* y_bf16, int64_t ldy) {
+  if (m < 1 || m > 8 || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0 || ldy < n) return PLQ_ERR_SHAPE;
+  if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
+  if (k_lo + k_hi > 32768 * 8 || n > (1 << 30)) return PLQ_ERR_LIMIT;
+  if (!y_bf16) return PLQ_ERR_NULL;
+  if (k_lo && (!a_lo_codes || !a_lo_sf || !b_lo_codes || !b_lo_sf)) return PLQ_ERR_NULL;
+  if (k_hi && (!a_hi_codes || !a_hi_sf || !b_hi_codes || !b_hi_sf)) return PLQ_ERR_NULL;
+  if (!aligned16(a_lo_codes) || !aligned16(b_lo_codes) || !aligned16(a_hi_codes) || !aligned16(b_hi_codes) ||
+      !aligned16(a_lo_sf) || !aligned16(b_lo_sf))
+    return PLQ_ERR_ALIGN;
+  return device_check();
+}
+
 }  // namespace plq
 
 extern "C" int64_t plq_gemv_workspace_bytes(int64_t n) { return n > 0 ? plq::gemv_ws_bytes(n) : 0; }
@@ -347,17 +364,10 @@ extern "C" int plq_gemv(const void* a_lo_codes, const void* a_lo_sf, const void*
                         int64_t m, int64_t n, int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy,
                         void* workspace, int64_t workspace_bytes, void* stream) {
   using namespace plq;
-  if (m < 1 || m > 8 || n < 1 || k_lo < 0 || k_hi < 0 || k_lo + k_hi <= 0 || ldy < n) return PLQ_ERR_SHAPE;
-  if (k_lo % 64 != 0 || k_hi % 32 != 0) return PLQ_ERR_SHAPE;
-  if (k_lo + k_hi > 32768 * 8 || n > (1 << 30)) return PLQ_ERR_LIMIT;
-  if (!y_bf16) return PLQ_ERR_NULL;
-  if (k_lo && (!a_lo_codes || !a_lo_sf || !b_lo_codes || !b_lo_sf)) return PLQ_ERR_NULL;
-  if (k_hi && (!a_hi_codes || !a_hi_sf || !b_hi_codes || !b_hi_sf)) return PLQ_ERR_NULL;
-  if (!aligned16(a_lo_codes) || !aligned16(b_lo_codes) || !aligned16(a_hi_codes) || !aligned16(b_hi_codes) ||
-      !aligned16(a_lo_sf) || !aligned16(b_lo_sf) || !aligned16(workspace))
-    return PLQ_ERR_ALIGN;
-  int st = device_check();
+  int st = check_gemv_args(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf, m, n, k_lo,
+                           k_hi, y_bf16, ldy);
   if (st != PLQ_OK) return st;
+  if (!aligned16(workspace)) return PLQ_ERR_ALIGN;
 
   GemvArgs a;
   a.a_lo = static_cast<const uint8_t*>(a_lo_codes); a.a_lo_sf = static_cast<const uint8_t*>(a_lo_sf);
@@ -413,8 +423,9 @@ constexpr int64_t kGemvStaticBytes = ((kGemvStaticMaxRows / 16 * 4 + 255) / 256)
 static __device__ __align__(256) unsigned char g_gemv_scratch[kGemvStaticBytes];   // ~8.4 MB; zero at load
 
 // In host code `g_gemv_scratch` is only a handle for the runtime, not an address a kernel can use:
-// the device address is looked up once per device, with that device current.
-static void* g_gemv_scratch_ptr[64];
+// the device address is looked up once per device, with that device current, and published atomically
+// (two host threads that both make the first call on a device resolve the same address).
+static std::atomic<void*> g_gemv_scratch_ptr[64];
 }  // namespace plq
 
 extern "C" int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_sf, const void* a_hi_codes,
@@ -422,19 +433,23 @@ extern "C" int plq_gemv_static_scratch(const void* a_lo_codes, const void* a_lo_
                                        const void* b_hi_codes, const void* b_hi_sf, int64_t m, int64_t n,
                                        int64_t k_lo, int64_t k_hi, void* y_bf16, int64_t ldy, void* stream) {
   using namespace plq;
+  // every check first (shapes, pointers, device): a rejected call touches nothing
+  const int st = check_gemv_args(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf, m, n,
+                                 k_lo, k_hi, y_bf16, ldy);
   if (n > kGemvStaticMaxRows) return PLQ_ERR_LIMIT;    // built-in scratch covers n <= 32768 only
+  if (st != PLQ_OK) return st;
   int dev = 0;
   PLQ_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PLQ_ERR_LIMIT;
-  if (g_gemv_scratch_ptr[dev] == nullptr) {
+  void* ptr = g_gemv_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     // first call on this device: resolve the array's device address and make sure the tickets start at
     // zero (they do at load; the kernel leaves them zero after every call)
-    void* ptr = nullptr;
     PLQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_gemv_scratch));
     PLQ_CUDA_TRY(cudaMemsetAsync(ptr, 0, ((gemv_ws_capacity(kGemvStaticBytes) * 4 + 255) / 256) * 256,
                                  static_cast<cudaStream_t>(stream)));
-    g_gemv_scratch_ptr[dev] = ptr;
+    g_gemv_scratch_ptr[dev].store(ptr, std::memory_order_release);
   }
   return plq_gemv(a_lo_codes, a_lo_sf, a_hi_codes, a_hi_sf, b_lo_codes, b_lo_sf, b_hi_codes, b_hi_sf, m, n, k_lo, k_hi,
-                  y_bf16, ldy, g_gemv_scratch_ptr[dev], kGemvStaticBytes, stream);
+                  y_bf16, ldy, ptr, kGemvStaticBytes, stream);
 }

@@ -76,10 +76,10 @@ def test_gemv_tc_against_oracle(m, n, k, k_hi):
     assert r <= TOL, r
 
 
-@pytest.mark.parametrize("m", [8, 16])
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 16])
 @pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
 def test_llama8b_shapes_gemv_tc(n, k, m):
-    """Full decode shapes at m = 8 and 16: agreement with the fused GEMM on the identical operands, a sample of
+    """Full decode shapes at m = 1, 2, 4, 8 and 16: agreement with the fused GEMM on the identical operands, a sample of
     output columns against the oracle, and run-to-run determinism."""
     k_hi = k // 32
     xc, wc = synth_activation(m, k, seed=42).cuda(), synth_weight(n, k, seed=n // 7 + k).cuda()

@@ -103,27 +103,35 @@ def test_config0_single_linear_against_reference_fixture(golden_dir):
     plq.check_device_status()
     ref = F.round_to_bf16(g["y_f32"])
     r = rel_l2(y, ref)
-    # the rotation's float32 summation order differs from torch's (a bf16 ulp on ~1e-3 of the
-    # rotated inputs), which moves a few codes: allow that on top of the kernel tolerance
-    assert r <= 3e-3, r
+    # the rotation's float32 summation order differs from torch's (a bf16 ulp on a small share of the rotated
+    # inputs), which could move a code.  The measured value and the number of codes that moved against the
+    # reference's own rotated activations are printed (measured on B200: 3.1e-4 and 0 of 65536).
+    ref_codes = F.pack_mixed(F.bf16_bits_to_f32(g["xr"]), 128)
+    mine = packed_to_numpy(pa)
+    moved = int((F.unpack_nibbles(mine["lo_codes"]) != F.unpack_nibbles(ref_codes["lo_codes"])).sum()) + \
+        int((mine["hi_codes"] != ref_codes["hi_codes"]).sum())
+    print(f"config 0 end to end: rel-L2 {r:.3e} against the reference's product; {moved} of {16 * 4096} activation "
+          f"codes differ from those of the reference's rotated input")
+    assert r <= TOL, r
     # with the reference's own rotated activations the input-side slack disappears
     pa2 = plq.pack(from_bits(g["xr"]), 128, hadamard=False, sf_layout="tiled")
     want = _oracle_bf16(packed_to_numpy(pa2), packed_to_numpy(pb))
     assert rel_l2(f32_of(plq.mixed_gemm(pa2, pb)), want) <= TOL
 
 
+@pytest.mark.parametrize("m", [512, 2048, 8192])
 @pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
-def test_prefill_full_size_properties(n, k):
-    """M = 8192 on the four Llama-3-8B shapes (the down projection runs the banded tile order): sampled rows
-    against the oracle, identical rows whatever the M they are computed in (tiles are independent),
-    determinism, clean status."""
-    m, k_hi = 8192, k // 32
+def test_prefill_full_size_properties(n, k, m):
+    """M = 512, 2048, 8192 on the four Llama-3-8B shapes, tile shape chosen by the library (the down projection
+    at M = 8192 runs the banded tile order): sampled rows against the oracle, identical rows whatever the M they
+    are computed in (tiles are independent), determinism, clean status."""
+    k_hi = k // 32
     x = synth_activation(m, k, seed=3000)
     w = synth_weight(n, k, seed=3001)
     pa = plq.pack(x.cuda(), k_hi, hadamard=True, sf_layout="tiled")
     pb = plq.pack(w.cuda(), k_hi, hadamard=True, sf_layout="tiled")
-    y1 = plq.mixed_gemm(pa, pb)
-    y2 = plq.mixed_gemm(pa, pb)
+    y1 = plq.mixed_gemm(pa, pb, variant=None)
+    y2 = plq.mixed_gemm(pa, pb, variant=None)
     plq.check_device_status()
     assert torch.equal(y1, y2)
     sel = np.sort(np.random.default_rng(1).choice(m, 12, replace=False))
@@ -133,6 +141,31 @@ def test_prefill_full_size_properties(n, k):
     assert rel_l2(f32_of(y1)[sel], want) <= TOL
     ps = plq.pack(x[:256].cuda(), k_hi, hadamard=True, sf_layout="tiled")
     assert torch.equal(plq.mixed_gemm(ps, pb), y1[:256])
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (4096, 14336)])
+def test_full_size_chain_from_bf16_against_oracle(n, k):
+    """The whole chain at full K: bf16 X and W -> QuantizedLinear (rotation, quantiser, packed GEMM) -> y, against
+    the oracle computed from the same bf16 tensors (its own rotation and quantiser, float32 product): sampled
+    token rows x sampled output rows, prefill (M = 2048, GEMM) and decode (M = 8, tensor-core GEMV)."""
+    from plaquant_b200.quantize import QuantizedLinear
+    k_hi = k // 32
+    x = synth_activation(2048, k, seed=4100 + k)
+    w = synth_weight(n, k, seed=4200 + n)
+    lin = QuantizedLinear.from_weight(w.cuda(), 1.0 / 32, rotate=True, online_had=True)
+    rows = np.sort(np.random.default_rng(3).choice(2048, 10, replace=False))
+    cols = np.sort(np.random.default_rng(4).choice(n, 96, replace=False))
+    want_x = F.prepare_activation(f32_of(x)[rows], k_hi, hadamard=True)
+    want_w = F.prepare_activation(f32_of(w)[cols], k_hi, hadamard=True)
+    want = F.round_to_bf16(F.linear(want_x, want_w))
+    y = f32_of(lin(x.cuda()))
+    plq.check_device_status()
+    r = rel_l2(y[np.ix_(rows, cols)], want)
+    assert r <= TOL, r
+    y8 = f32_of(lin(x[rows[:8]].cuda()))
+    plq.check_device_status()
+    r8 = rel_l2(y8[:, cols], want[:8])
+    assert r8 <= TOL, r8
 
 
 def test_argument_errors():

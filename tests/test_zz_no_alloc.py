@@ -40,6 +40,20 @@ def test_static_scratch_gemv_equals_workspace_gemv_twice_in_a_row():
     assert torch.equal(got1, want1) and torch.equal(got2, want2) and torch.equal(got1_again, want1)
 
 
+def test_static_scratch_gemv_with_changing_widths_and_at_its_maximum():
+    """Calls of different N share the one array: a wide call (N = 28672) followed by a narrow one (N = 4096) and
+    the widest the entry point accepts (N = 32768), each against plq_gemv with a caller's workspace."""
+    k, k_hi = 4096, 128
+    x = plq.pack(synth_activation(4, k, seed=80).cuda(), k_hi, hadamard=True, sf_layout="rowmajor")
+    ws = {n: plq.pack(synth_weight(n, k, seed=81 + n % 7).cuda(), k_hi, hadamard=True, sf_layout="rowmajor")
+          for n in (28672, 4096, 32768)}
+    want = {n: plq.gemv(x, w) for n, w in ws.items()}
+    for n in (28672, 4096, 32768, 4096, 28672):
+        got = _static_gemv(x, ws[n])
+        torch.cuda.synchronize()
+        assert torch.equal(got, want[n]), n
+
+
 def test_static_scratch_rejects_sizes_beyond_its_maximum():
     from plaquant_b200 import _lib
     x = plq.pack(synth_activation(1, 128, seed=1).cuda(), 64, sf_layout="rowmajor")
