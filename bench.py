@@ -15,11 +15,18 @@ is far larger than the 126 MB L2, so no explicit flush is needed between iterati
 
 `value` is GEMM+pack throughput with inputs resident in HBM; `e2e` is the same step driven
 from pinned host buffers (host->device copy of both activation matrices and device->host copy
-of the down-projection output inside the timed region).  With N > 1 every rank runs the same
-step on its own GPU (the per-op configurations do not shard: replicas only, weak scaling).
+of the down-projection output inside the timed region; the other three outputs are inputs of later
+kernels in a real layer and would never leave the device, so only the layer's last output is read
+back).  With N > 1 every rank runs the same step on its own GPU (the per-op configurations do not
+shard: replicas only, weak scaling).  After the headline step every run, at every N, also runs the
+configuration that does shard - the tensor-parallel decoder stack (`model_tp` in the JSON line:
+strong scaling over the N ranks, column-/row-parallel linears, one all-reduce per row-parallel linear).
 
-`--impl reference` times the CPU restatement of the reference's fake-quant path
-(oracle/plq_oracle.c, OpenMP, all host threads) on a bounded sample of the same workload.
+`--impl reference` times the reference's own CPU code for the path on a bounded sample of the same
+workload, with all host threads: its ActQuantizer (NVFP4 + MXFP8) and Hadamard matrix from the staged
+copy under oracle/_ref (see oracle/build_ref.py) followed by torch's bf16 F.linear, as the reference's
+fake-quant forward does; when oracle/_ref is absent, the C port oracle/plq_oracle.c instead.
+The one JSON line on stdout is kept short; the full per-case tables go to stderr as a second JSON line.
 """
 from __future__ import annotations
 
@@ -39,6 +46,7 @@ SHAPES = [("qkv", 4096, 6144, True), ("o", 4096, 4096, False), ("gate_up", 4096,
 M_TOKENS = 8192
 NOMINAL_FP4_TFLOPS = 9000.0     # B200 dense FP4 (NVIDIA's sparse figure halved)
 NOMINAL_HBM_GBS = 8000.0
+GEMM_QKV_DRAM_BYTES = 90.8e6       # ncu: dram bytes read + written by one QKV-shape GEMM launch (profiles/)
 
 
 def flops_of(m, shapes=SHAPES):
@@ -112,53 +120,103 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# reference arm: the CPU port of the reference's fake-quant path, bounded sample
+# CPU arm: the reference's own code (oracle/_ref) or, without it, the C port; bounded sample
 # ------------------------------------------------------------------------------------------------
 SAMPLE_M, SAMPLE_N = 256, 2048
 
 
-def run_cpu_sample(steps: int, warmup: int):
-    """Times [RMSNorm] + Hadamard + fake-quant pack of SAMPLE_M activation rows and the float32
-    product with SAMPLE_N pre-quantised weight rows, for each of the four shapes (full K)."""
-    import numpy as np
-    import torch
-    from oracle import cport
-    # all host threads, whatever a launcher exported for its workers (torchrun sets OMP_NUM_THREADS=1)
-    cport.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+def host_threads() -> int:
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
-    def bits(t):
-        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
 
+def _sample_tensors(torch):
     g = torch.Generator().manual_seed(1234)
-    work = []
+    out = []
     for name, k, n, norm in SHAPES:
         x = torch.randn(SAMPLE_M, k, generator=g)
         x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
         w = torch.randn(SAMPLE_N, k, generator=g) * 0.02
         gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
-        pw = cport.prepare(bits(w.to(torch.bfloat16)), k // 32, hadamard=True)      # weight prep: once, untimed
-        wdq = cport.dequant(pw)
-        work.append((bits(x.to(torch.bfloat16)), bits(gamma) if norm else None, k, wdq))
-    import ctypes
-    lib = cport.lib()
+        out.append((name, k, x.to(torch.bfloat16), w.to(torch.bfloat16), gamma if norm else None))
+    return out
+
+
+def _cpu_step_reference(torch):
+    """One step = for each of the four shapes: [RMSNorm] -> block-Hadamard(128) as a float32 matmul with the
+    reference's own matrix -> the reference's ActQuantizer (bits "nvfp4", high_bits "mxfp8", last K/32 channels)
+    -> torch's bf16 F.linear against weights the reference's quantiser prepared once (untimed)."""
+    import torch.nn.functional as Fn
+    from oracle import build_ref
+    qu, get_hadamard_matrix = build_ref.load()
+    torch.set_num_threads(host_threads())
+    h128 = get_hadamard_matrix(128, "cpu").float()
+
+    def rotate(t):
+        k = t.shape[-1]
+        return (t.float().view(-1, k // 128, 128) @ h128).view(-1, k).to(t.dtype)
+
+    work = []
+    with torch.no_grad():
+        for name, k, x, w, gamma in _sample_tensors(torch):
+            k_hi = k // 32
+            wr = rotate(w)
+            wq = torch.cat([qu.fake_quantize_nvfp4(wr[:, : k - k_hi]), qu.fake_quantize_mxfp8(wr[:, k - k_hi:])], -1)
+            q = qu.ActQuantizer()
+            q.configure(bits="nvfp4", high_bits="mxfp8", high_bits_length=k_hi)
+            work.append((x, gamma, q, wq.to(torch.bfloat16)))
+
+    def step():
+        with torch.no_grad():
+            for x, gamma, q, wq in work:
+                if gamma is not None:           # inference/forward_pass.py:33-39 of the reference
+                    xf = x.float()
+                    x = (gamma.float() * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6))).to(x.dtype)
+                Fn.linear(q(rotate(x)), wq)
+    return step, "reference", torch.get_num_threads()
+
+
+def _cpu_step_port(torch):
+    """The same step on the C port (oracle/plq_oracle.c, OpenMP) with torch's float32 matmul for the product."""
+    import numpy as np
+    from oracle import cport
+    cport.set_num_threads(host_threads())
+    torch.set_num_threads(host_threads())
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    work = []
+    for name, k, x, w, gamma in _sample_tensors(torch):
+        wdq = torch.from_numpy(cport.dequant(cport.prepare(bits(w), k // 32, hadamard=True)))
+        work.append((bits(x), None if gamma is None else bits(gamma), k, wdq))
 
     def step():
         for xb, gb, k, wdq in work:
-            px = cport.prepare(xb, k // 32, gb, 1e-6, True)
-            a = cport.dequant(px)
-            y = np.empty((SAMPLE_M, SAMPLE_N), np.float32)
-            lib.plqo_matmul_nt(a.ctypes.data_as(ctypes.c_void_p), wdq.ctypes.data_as(ctypes.c_void_p), SAMPLE_M,
-                               SAMPLE_N, k, y.ctypes.data_as(ctypes.c_void_p))
+            a = torch.from_numpy(cport.dequant(cport.prepare(xb, k // 32, gb, 1e-6, True)))
+            torch.matmul(a, wdq.T)
+    return step, "port", cport.num_threads()
+
+
+def run_cpu_sample(steps: int, warmup: int, budget_s: float = 60.0):
+    """Times the CPU arm on SAMPLE_M token rows x SAMPLE_N weight rows of each of the four shapes (full K); stops
+    early once `budget_s` seconds of timed work are done, and says how many steps it timed."""
+    import torch
+    from oracle import build_ref
+    step, kind, cores = (_cpu_step_reference if build_ref.available() else _cpu_step_port)(torch)
     for _ in range(warmup):
         step()
-    t0 = time.perf_counter()
-    for _ in range(steps):
+    done, t0 = 0, time.perf_counter()
+    while done < steps and (done == 0 or time.perf_counter() - t0 < budget_s):
         step()
-    dt = (time.perf_counter() - t0) / max(steps, 1)
+        done += 1
+    dt = (time.perf_counter() - t0) / done
     fl = sum(2.0 * SAMPLE_M * SAMPLE_N * k for _, k, _, _ in SHAPES)
-    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cport.num_threads(), "kind": "port",
-            "sample": f"{SAMPLE_M} token rows x {SAMPLE_N} weight rows of each of the 4 shapes, full K, "
-                      f"pack + float32 product, weight quantisation excluded", "ms_per_step": dt * 1e3}
+    what = ("the reference's ActQuantizer + Hadamard matrix (oracle/_ref) and torch bf16 F.linear" if kind == "reference"
+            else "C port oracle/plq_oracle.c + torch float32 matmul (oracle/_ref not staged)")
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"{SAMPLE_M} token rows x {SAMPLE_N} weight rows of each of the 4 shapes, full K, [RMSNorm] + "
+                      f"rotation + activation quantiser + product per step, weight quantisation excluded; {what}",
+            "ms_per_step": dt * 1e3, "steps_timed": done}
 
 
 def config_dict(n_gpus):
@@ -171,10 +229,10 @@ def config_dict(n_gpus):
 def main_reference(args, rank):
     if rank != 0:
         return
-    steps = max(min(args.steps, 40), 1)      # a step is ~0.15-0.3 s of host work: keep the arm within a minute or so
-    b = run_cpu_sample(steps, min(args.warmup, 2))
+    warm = min(args.warmup, 2)
+    b = run_cpu_sample(max(args.steps, 1), warm, budget_s=90.0)   # a step is 0.1-1 s of host work
     line = {"impl": "reference", "metric": "mixed NVFP4/MXFP8 GEMM TFLOP/s", "value": b["value"], "unit": "TFLOP/s",
-            "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": b["ms_per_step"],
+            "n_gpus": args.gpus, "steps": b["steps_timed"], "warmup": warm, "ms_per_step": b["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)",
             "data": "synthetic", "config": config_dict(args.gpus),
             "cpu_baseline": {k: b[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -316,6 +374,14 @@ def main_ours(args, rank, local_rank, world):
     if rank == 0:
         extra = side_benchmarks(plq, torch, dev, peaks)
 
+    # free the per-op operands, then the configuration that shards: the tensor-parallel decoder stack
+    model_tp = None
+    if args.tp_layers > 0:
+        for L in layers:
+            L["pw"] = L["pa"] = L["y"] = None
+        x_dev.clear(); x_in.clear()
+        torch.cuda.empty_cache()
+        model_tp = run_model_tp(args, torch, plq, rank, world, dev, peaks)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
@@ -323,7 +389,13 @@ def main_ours(args, rank, local_rank, world):
     if rank != 0:
         return
     gemm_tflops = fl / (gemm_ms * 1e-3) / 1e12
-    fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+    # Comparator: no FP4 peak is measured on this pool, so the tensor roofline is 4 x the measured cuBLAS bf16 rate
+    # (FP4 is nominally 4 x bf16): the burst figure when the timed region is shorter than a second (the SM clock
+    # has not settled under the power cap yet), the sustained one otherwise.
+    timed_s = ms_step * 1e-3 * args.steps
+    which = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+    fp4_peak = 4.0 * peaks[which]
+    per_gemm_ms = {k: sum(v) / len(v) for k, v in per_gemm.items()}
     line = {
         "metric": "mixed NVFP4/MXFP8 GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -335,24 +407,123 @@ def main_ours(args, rank, local_rank, world):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "mixed_gemm_kernel<256, 2>", "achieved": gemm_tflops,
                      "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
-                     "peak_source": f"4 x {peaks['source']} cuBLAS bf16 sustained ({peaks['bf16_tflops_sustained']} TF/s); "
-                                    "no FP4 peak is measured on this pool",
+                     "peak_source": f"4 x {peaks['source']} cuBLAS {which} ({peaks[which]} TF/s; timed region "
+                                    f"{timed_s:.2f} s); no FP4 peak is measured on this pool",
                      "frac_of_nominal_fp4": gemm_tflops / NOMINAL_FP4_TFLOPS, "nominal_fp4_tflops": NOMINAL_FP4_TFLOPS,
-                     "flops_per_step": fl, "gemm_ms_per_step": gemm_ms,
-                     "per_gemm_ms": {k: sum(v) / len(v) for k, v in per_gemm.items()},
-                     "per_gemm_tflops": {L["name"]: 2.0 * M_TOKENS * L["n"] * L["k"] / (sum(per_gemm[L["name"]]) / len(per_gemm[L["name"]]) * 1e-3) / 1e12 for L in layers},
-                     "traffic": 90.8e6,
+                     "flops_per_step": fl, "gemm_ms_per_step": gemm_ms, "pack_ms_per_step": ms_step - gemm_ms,
+                     "per_gemm_tflops": {L["name"]: round(2.0 * M_TOKENS * L["n"] * L["k"] / (per_gemm_ms[L["name"]] * 1e-3) / 1e12, 1)
+                                         for L in layers},
+                     "traffic": GEMM_QKV_DRAM_BYTES,
                      "traffic_note": "dram__bytes_read+write of one QKV-shape launch (412 GFLOP, 134.6 MB of operands "
                                      "and output) from the ncu capture in profiles/; part of the output is still in L2 "
                                      "when the kernel ends"},
-        **extra,
     }
+    detail = {"per_gemm_ms": per_gemm_ms, **extra}
+    # short forms of the side results for the one-line record
+    if "pack" in extra:
+        line["pack"] = {k: extra["pack"][k] for k in ("us", "gbs", "frac_of_measured_hbm", "frac_of_nominal_hbm")}
+    if "gemv" in extra:
+        gv = extra["gemv"]
+        line["gemv_m8"] = {name: {"us": round(gv[f"{name}_m8"]["us"], 2),
+                                  "frac_of_measured_hbm": round(gv[f"{name}_m8"]["frac_of_measured_hbm"], 3)}
+                           for name, _, _, _ in SHAPES}
+        tot_b = sum(gv[f"{name}_m8"]["bytes"] for name, _, _, _ in SHAPES)
+        tot_us = sum(gv[f"{name}_m8"]["us"] for name, _, _, _ in SHAPES)
+        line["gemv_m8"]["layer"] = {"us": round(tot_us, 2), "frac_of_measured_hbm": round(tot_b / tot_us / 1e3 / peaks["hbm_gbs"], 3)}
+    line["hbm_peak_gbs"] = {"measured": peaks["hbm_gbs"], "nominal": NOMINAL_HBM_GBS, "source": peaks["source"]}
+    if model_tp is not None:
+        line["model_tp"] = model_tp
     if world == 1:
         try:
-            line["cpu_baseline"] = {k: v for k, v in run_cpu_sample(3, 1).items() if k != "ms_per_step"}
-        except Exception as exc:  # the checker library could not be built on this host
+            line["cpu_baseline"] = {k: v for k, v in run_cpu_sample(20, 1, budget_s=15.0).items()
+                                    if k not in ("ms_per_step", "steps_timed")}
+        except Exception as exc:  # the checker could not be built or staged on this host
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
     print(json.dumps(line), flush=True)
+    print(json.dumps({"detail": detail}), file=sys.stderr, flush=True)
+
+
+def run_model_tp(args, torch, plq, rank, world, dev, peaks):
+    """configs[4] on the ranks of this run: the Llama-3-70B-architecture decoder stack (random init, `--tp-layers`
+    of its 80 layers), tensor-parallel over the N ranks (column-parallel QKV / gate_up, row-parallel O / down, one
+    all-reduce per row-parallel linear; decode batches reduce inside the RMSNorm-quant kernel over peer memory),
+    batch 16, 2048 prefill tokens + 128 greedy decode steps.  Strong scaling: the job is fixed.  Returns the
+    `model_tp` block (rank 0) or None."""
+    import torch.distributed as dist
+    from plaquant_b200 import tp
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+    ctx = tp.TPContext(rank, world, None)
+    cfg = LlamaConfig.llama3_70b()
+    layers = args.tp_layers
+    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0)
+    batch, prefill, decode = args.batch, args.prefill, args.decode
+    ids = torch.randint(0, cfg.vocab_size, (batch, prefill), generator=torch.Generator().manual_seed(40)).to(dev)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+    out = model.generate(ids, decode)                # warm-up run (also builds the caches' allocator pools)
+    plq.check_device_status()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    out = model.generate(ids, decode)
+    e1.record()
+    sync()
+    plq.check_device_status()
+    ms = e0.elapsed_time(e1)
+    tev = model.timing_events
+    prefill_ms, decode_ms = tev[0].elapsed_time(tev[1]), tev[1].elapsed_time(tev[2])
+    same = True
+    ar = {}
+    if world > 1:
+        t = torch.tensor([ms, prefill_ms, decode_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, prefill_ms, decode_ms = (float(v) for v in t.tolist())
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(g, gathered[0]) for g in gathered)
+        # the all-reduces of the path, timed alone: 2 per layer, [batch * prefill, hidden] bf16 in the prefill
+        # (NCCL) and [batch, hidden] per decode step (inside the fused kernel unless --nccl-reduce)
+        for name, rows, reps in (("prefill", batch * prefill, 4), ("decode", batch, 50)):
+            buf = torch.zeros(rows, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+            dist.all_reduce(buf)
+            sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                dist.all_reduce(buf)
+            b.record()
+            sync()
+            ar[name] = {"bytes_per_allreduce": buf.numel() * 2, "nccl_ms_each": a.elapsed_time(b) / reps,
+                        "per_pass": 2 * layers}
+            del buf
+        ar["prefill"]["share_of_prefill_ms"] = ar["prefill"]["nccl_ms_each"] * 2 * layers / prefill_ms
+    # bytes one decode step must read on a rank: packed weights of the linears (tiled copy), the unquantised LM
+    # head, and the key/value caches up to the current position (mean over the decode steps)
+    w_bytes = sum(lin._gemm_w.nbytes() for L in model.layers for lin in (L.qkv, L.o, L.gate_up, L.down))
+    head_bytes = model.lm_head.numel() * 2
+    kv_bytes = layers * 2 * batch * (prefill + decode / 2) * model.kv_heads * cfg.head_dim * 2
+    step_ms = decode_ms / decode
+    step_bytes = w_bytes + head_bytes + kv_bytes
+    del model
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    tokens = batch * (prefill + decode)
+    return {"metric": "decoder tokens/s (prefill + greedy decode)", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "scaling": "strong", "parallelism": f"tp{world}", "layers": layers, "of_layers": cfg.num_layers,
+            "batch": batch, "prefill_tokens": prefill, "decode_steps": decode, "ms": ms, "prefill_ms": prefill_ms,
+            "decode_ms": decode_ms, "decode_ms_per_step": step_ms, "ranks_agree_on_tokens": same,
+            "reduce": "fused into the RMSNorm-quant kernel over peer memory (decode), NCCL (prefill)" if (args.fused_reduce and world > 1)
+                      else ("NCCL" if world > 1 else "none (one rank)"),
+            "allreduce": ar,
+            "decode_roofline": {"bound": "hbm", "bytes_per_step_per_rank": step_bytes,
+                                "packed_weight_bytes": w_bytes, "lm_head_bytes": head_bytes, "kv_cache_bytes": kv_bytes,
+                                "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": step_bytes / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
 
 
 def main_model(args, rank, local_rank, world):
@@ -601,6 +772,8 @@ def main():
     ap.add_argument("--workload", default="linears", choices=["linears", "model"],
                     help="linears: the per-op step (default); model: the tensor-parallel decoder stack")
     ap.add_argument("--layers", type=int, default=None, help="model workload: number of decoder layers (default 80)")
+    ap.add_argument("--tp-layers", type=int, default=16,
+                    help="layers of the 80-layer decoder stack in the model_tp block of the default run (0 = skip it)")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--decode", type=int, default=128)

@@ -53,6 +53,7 @@ extern "C" {
 #define PLQ_ERR_TENSORMAP  -6   /* cuTensorMapEncodeTiled rejected a descriptor */
 #define PLQ_ERR_LIMIT      -7   /* size beyond a documented maximum */
 #define PLQ_DEV_TIMEOUT     1   /* written by a kernel: a bounded wait ran out */
+#define PLQ_DEV_PROTOCOL    2   /* written by a kernel: a fused reduction was called on the wrong buffer set */
 
 #define PLQ_SF_ROWMAJOR 0
 #define PLQ_SF_TILED    1
@@ -129,14 +130,23 @@ PLQ_API int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf16, 
  *   peer_flags_dev  device array [world] of addresses: rank r's int32 flags[world]
  *   flags, sync     this rank's flags[world] and int32 sync[2], zero before the first call, owned by the library
  *                   afterwards
- * Every rank must make the same sequence of calls; call sites must alternate between two sets of x buffers
- * (a rank may be one call ahead of a peer that is still reading).  A rank that does not show up within the
- * bounded wait makes the others store PLQ_DEV_TIMEOUT to `dev_status` and finish (their output is then void).
+ *   buffer_index    which of the caller's two sets of x buffers `peer_x_dev` names (0 or 1; -1 = not checked)
+ * Every rank must make the same sequence of calls, and consecutive calls must alternate between two sets of x
+ * buffers, starting with set 0: a rank may be one call ahead of a peer that is still reading, and it is the
+ * alternation alone (no other collective is needed in between) that keeps it from overwriting what the peer
+ * reads - rank r writes set b again only after its call in between has seen every peer announce that call,
+ * i.e. after every peer has finished the earlier call on set b.  The kernel numbers the calls itself (in
+ * `sync`); call c must use set (c + 1) % 2, counting from c = 1.  A CUDA graph that is replayed must therefore
+ * contain an even number of these calls, or a replay would reuse the set of the call just before it: the kernel
+ * checks `buffer_index` against its own count and stores PLQ_DEV_PROTOCOL to `dev_status` on a mismatch (the
+ * output is then void).  A rank that does not show up within the bounded wait makes the others store
+ * PLQ_DEV_TIMEOUT to `dev_status` and finish (their output is then void).
  * Replaces `dist.all_reduce` + `x = residual + x; x = rms_norm(x, ...)` + the next quantiser in a
  * tensor-parallel decoder layer (inference/forward_pass.py:258-264 under tensor parallelism).
  */
 PLQ_API int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev, int32_t* flags,
-                                           int32_t* sync, int world, int rank, const void* residual_bf16,
+                                           int32_t* sync, int world, int rank, int buffer_index,
+                                           const void* residual_bf16,
                                            void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
                                            int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
                                            void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,

@@ -49,6 +49,7 @@ extern "C" const char* plq_status_string(int status) {
     case PLQ_ERR_TENSORMAP: return "cuTensorMapEncodeTiled rejected a tensor map";
     case PLQ_ERR_LIMIT: return "a size exceeds a documented maximum";
     case PLQ_DEV_TIMEOUT: return "a bounded wait inside a kernel ran out; the output is undefined";
+    case PLQ_DEV_PROTOCOL: return "a fused reduction was called on the wrong one of its two buffer sets (calls must alternate; a replayed CUDA graph must hold an even number of them); the output is undefined";
     default: return "unknown status";
   }
 }

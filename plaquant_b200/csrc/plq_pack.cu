@@ -47,6 +47,7 @@ struct PackArgs {
   int* sync;                     // this rank's {calls completed, CTAs finished in the current call}
   int32_t* status;               // receives PLQ_DEV_TIMEOUT if a rank does not show up
   int world, rank;
+  int buffer_index;              // which of the two buffer sets peer_x names (0 / 1), or -1: checked against the call count
   const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
   float eps;
   int rows, k, k_lo;     // k_hi = k - k_lo
@@ -236,6 +237,10 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     // every block waits (bounded) until all peers have announced c in this rank's flags.  Buffers alternate
     // between two per call site order, so a peer that runs ahead never overwrites what is being read here.
     const int call = *reinterpret_cast<volatile int*>(a.sync) + 1;
+    // call c reads buffer set (c + 1) % 2; anything else means the caller broke the alternation (for instance a
+    // replayed graph with an odd number of calls) and a peer may still be reading the set that was just rewritten
+    if (blockIdx.x == 0 && tid == 0 && a.buffer_index >= 0 && ((call + 1) & 1) != a.buffer_index)
+      atomicExch(a.status, PLQ_DEV_PROTOCOL);
     if (blockIdx.x == 0 && tid < a.world) {
       __threadfence_system();
       asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flags[tid] + a.rank), "r"(call) : "memory");
@@ -598,7 +603,7 @@ struct PeerArgs {
   int32_t* flags;
   int32_t* sync;
   int32_t* status;
-  int world, rank;
+  int world, rank, buffer_index;
 };
 
 static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int64_t ldx, const void* gamma, float eps,
@@ -623,12 +628,12 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.h_out = static_cast<uint4*>(h_out);
   a.ldx8 = static_cast<int>(ldx / 8);
   a.peer_x = nullptr; a.peer_flags = nullptr; a.flags = nullptr; a.sync = nullptr; a.status = nullptr;
-  a.world = 1; a.rank = 0;
+  a.world = 1; a.rank = 0; a.buffer_index = -1;
   if (peers) {
     a.peer_x = reinterpret_cast<const uint4* const*>(peers->peer_x);
     a.peer_flags = reinterpret_cast<int* const*>(peers->peer_flags);
     a.flags = peers->flags; a.sync = peers->sync; a.status = peers->status;
-    a.world = peers->world; a.rank = peers->rank;
+    a.world = peers->world; a.rank = peers->rank; a.buffer_index = peers->buffer_index;
   }
   a.gamma = static_cast<const uint4*>(gamma);
   a.eps = eps;
@@ -730,14 +735,16 @@ extern "C" int plq_add_rmsnorm_pack(const void* x_bf16, const void* residual_bf1
 }
 
 extern "C" int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev, int32_t* flags,
-                                              int32_t* sync, int world, int rank, const void* residual_bf16,
+                                              int32_t* sync, int world, int rank, int buffer_index,
+                                              const void* residual_bf16,
                                               void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
                                               int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
                                               void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
                                               void* stream) {
   if (!gamma_bf16) return PLQ_ERR_NULL;
   if (rows < 1) return PLQ_ERR_SHAPE;               // every rank must launch, or the others wait for it
-  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank};
+  if (buffer_index < -1 || buffer_index > 1) return PLQ_ERR_SHAPE;
+  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank, buffer_index};
   return plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
                           lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
 }

@@ -194,10 +194,20 @@ class ResQForwardB200:
             h, pa = ops.add_rmsnorm_pack(o, h, L.ln2, c.rms_eps, self.k_hi_hidden)      # h += o; RMSNorm(ln2); quantise
         gu = L.gate_up(pa)                                                              # [b*t, 2*ffn] = [gate | up]
         pa = ops.silu_mul_pack(gu, self.k_hi_ffn)                                       # SiLU(gate)*up; rotate; quantise
-        if fused and li + 1 < len(self.layers):
-            L.down(pa, out=self.peer.buffer(b * t))                                     # reduced by the next layer's first kernel
+        if fused:
+            L.down(pa, out=self.peer.buffer(b * t))       # reduced by the next layer's first kernel (or _finish)
             return h, _IN_PEER_BUFFER
         return h, self.ctx.all_reduce(L.down(pa)).view(b, t, -1)
+
+    def _finish(self, h: torch.Tensor, delta) -> torch.Tensor:
+        """Residual stream after the last layer: h + delta.  When the last MLP output is still waiting in the peer
+        buffers it is reduced by the same fused kernel as everywhere else (its packed output is not needed), which
+        also makes the number of fused calls per pass even: 2 per layer."""
+        if delta is _IN_PEER_BUFFER:
+            b, t, _ = h.shape
+            h, _ = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, self.final_norm, self.cfg.rms_eps, self.k_hi_hidden)
+            return h
+        return h + delta
 
     # ---- public ----------------------------------------------------------------------------------
     @torch.no_grad()
@@ -212,7 +222,7 @@ class ResQForwardB200:
         for li in range(len(self.layers)):
             h, delta = self._forward_layer(li, h, delta, pos0, cos_sin)
         self.pos = pos0 + input_ids.shape[1]
-        return self._logits(h[:, -1] + delta[:, -1])
+        return self._logits(self._finish(h, delta)[:, -1])
 
     def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
         """Final norm + unquantised LM head in the model dtype (inference/forward_pass.py:178-181 in the reference)."""
@@ -262,7 +272,7 @@ class ResQForwardB200:
             delta = None
             for li in range(len(self.layers)):
                 h, delta = self._forward_layer(li, h, delta, 0, cos_sin, static=st)
-            tok.copy_(self._logits(h[:, -1] + delta[:, -1]).argmax(-1, keepdim=True))
+            tok.copy_(self._logits(self._finish(h, delta)[:, -1]).argmax(-1, keepdim=True))
             st["pos"].add_(1)
             step_idx.add_(1)
 
@@ -275,12 +285,22 @@ class ResQForwardB200:
                 decode_step()                                                # step 1, eager on the capture stream
                 side.synchronize()
                 if steps > 2:
+                    calls_before = self.peer.calls if self.peer is not None else 0
                     with torch.cuda.graph(graph, stream=side):
                         decode_step()
             torch.cuda.current_stream(dev).wait_stream(side)
+            if self.peer is not None and steps > 2:
+                # a replayed step keeps the buffer set of each call site: sets alternate across replays only if the
+                # step holds an even number of fused reductions (two per layer)
+                assert (self.peer.calls - calls_before) % 2 == 0, "odd number of fused reductions in the decode step"
+                # ranks reach this point at different times (capture is ~2000 host launches): line them up so the
+                # bounded cross-rank wait of the first replay measures the peers, not the host skew
+                import torch.distributed as dist
+                dist.barrier(self.ctx.group)
             for _ in range(steps - 2):                                       # capture does not execute: steps 2 .. steps-1
                 graph.replay()
         ev[2].record()
+        ops.check_device_status(dev)                                         # a missing rank or a protocol error is loud
         self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. capture) = ev[1] -> ev[2], once synchronised
         self.pos = t_max
         return out

@@ -177,11 +177,12 @@ def allreduce_add_rmsnorm_pack(peer, rows: int, residual: torch.Tensor, gamma: t
     with torch.cuda.device(residual.device):
         st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
             _ptr(peer.peer_x[peer.next]), _ptr(peer.peer_flags), _ptr(peer.flags), _ptr(peer.sync), peer.world, peer.rank,
-            _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), rows, k, k_hi, int(hadamard),
+            peer.next, _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), rows, k, k_hi, int(hadamard),
             _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), p.sf_layout,
             _ptr(status_word(residual.device)), _stream(residual.device))
     _lib.check(st)
     peer.next ^= 1
+    peer.calls += 1
     return h.view(residual.shape), p
 
 

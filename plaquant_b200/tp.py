@@ -67,12 +67,23 @@ class TPContext:
 
 class PeerReduce:
     """Peer-memory plumbing of the fused all-reduce + residual + RMSNorm-quant kernel
-    (`ops.allreduce_add_rmsnorm_pack`): two symmetric bf16 [rows, k] buffers per rank for the partial outputs
-    (call sites alternate between them), a symmetric int32 flag array, a local call counter, and device arrays
-    with every rank's addresses.  Built on torch.distributed's symmetric memory (CUDA IPC / VMM mappings of the
-    other ranks' allocations on one node); the kernel itself only does plain peer loads and flag stores."""
+    (`ops.allreduce_add_rmsnorm_pack`): two symmetric bf16 [rows, k] buffer sets per rank for the partial outputs,
+    a symmetric int32 flag array, a local call counter, and device arrays with every rank's addresses.  Built on
+    torch.distributed's symmetric memory (CUDA IPC / VMM mappings of the other ranks' allocations on one node);
+    the kernel itself only does plain peer loads and flag stores, so the mappings are requested without an NVLink
+    multicast binding (TORCH_SYMM_MEM_DISABLE_MULTICAST).
+
+    Invariant.  Consecutive fused calls alternate between the two buffer sets, starting with set 0 (`next`), on
+    every rank alike.  That alone keeps a fast rank from overwriting what a slower peer still reads: before rank r
+    writes set b again it has completed the call in between, and that call waited until every peer had announced
+    it - which a peer does only after finishing its previous call, the one that read set b.  No other collective
+    is needed between the calls.  A decode step that is captured in a CUDA graph freezes `next` per call site, so
+    the step must contain an even number of fused calls (`calls` counts them; `ResQForwardB200.generate` checks);
+    the kernel verifies the set against its own call count and reports PLQ_DEV_PROTOCOL otherwise."""
 
     def __init__(self, rows: int, k: int, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # before the first symmetric allocation
         import torch.distributed._symmetric_memory as symm_mem
         group = group if group is not None else dist.group.WORLD
         self.rows, self.k, self.device = rows, k, torch.device(device)
@@ -90,7 +101,8 @@ class PeerReduce:
         self.peer_x = [torch.tensor([p + b * per_buf for p in xs], dtype=torch.int64, device=self.device) for b in range(2)]
         self.peer_flags = torch.tensor(fs, dtype=torch.int64, device=self.device)
         self.sync = torch.zeros(2, dtype=torch.int32, device=self.device)
-        self.next = 0
+        self.next = 0                                     # buffer set of the next fused call
+        self.calls = 0                                    # fused calls issued (or captured) so far
         torch.cuda.synchronize(self.device)
         dist.barrier(group)                               # nobody signals before every rank has zeroed its flags
 

@@ -88,7 +88,7 @@ def test_a_rank_that_never_announces_itself_gives_a_timeout_status_not_a_hang():
     h = torch.empty_like(res)
     p = ops.alloc_packed(rows, k, k_hi, "tiled", dev)
     st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
-        peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), 2, 0, res.data_ptr(), h.data_ptr(),
+        peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), 2, 0, 0, res.data_ptr(), h.data_ptr(),
         gamma.data_ptr(), 1e-6, rows, k, k_hi, 1, p.lo_codes.data_ptr(), p.lo_sf.data_ptr(), p.hi_codes.data_ptr(),
         p.hi_sf.data_ptr(), p.sf_layout, ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
     assert st == 0
@@ -124,7 +124,7 @@ def test_sum_over_emulated_ranks_on_one_gpu(world):
         h = torch.empty(rows, k, dtype=torch.bfloat16, device=dev)
         p = ops.alloc_packed(rows, k, k_hi, "rowmajor", dev)
         st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
-            peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, res_d.data_ptr(),
+            peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, -1, res_d.data_ptr(),
             h.data_ptr(), gamma_d.data_ptr(), 1e-6, rows, k, k_hi, 1, p.lo_codes.data_ptr(), p.lo_sf.data_ptr(),
             p.hi_codes.data_ptr(), p.hi_sf.data_ptr(), p.sf_layout, ops.status_word(dev).data_ptr(),
             torch.cuda.current_stream(dev).cuda_stream)
@@ -140,3 +140,81 @@ def test_sum_over_emulated_ranks_on_one_gpu(world):
         got = packed_to_numpy(p)
         for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
             assert np.array_equal(got[key], want[key]), key
+
+
+def test_replayed_graph_alternates_buffer_sets_and_an_odd_call_count_is_reported():
+    """A decode step replayed from a CUDA graph freezes which buffer set each call site reads.  With an even number
+    of fused reductions per graph the sets keep alternating across replays and every replay is bit-exact; a graph
+    with an odd number reuses the set of the call just before it on its second replay, which the kernel reports as
+    PLQ_DEV_PROTOCOL.  Two ranks emulated on one GPU: rank 1's buffers are local and its announcements are written
+    from the host before each replay."""
+    from oracle import formats as F
+    from plaquant_b200 import _lib, ops
+    from tests._util import f32_of, packed_to_numpy, synth_activation, synth_gamma
+    dev = torch.device("cuda", 0)
+    rows, k, k_hi, world = 4, 1024, 64, 2
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    sync = torch.zeros(2, dtype=torch.int32, device=dev)
+    peer_flags = torch.tensor([flags.data_ptr()] * world, dtype=torch.int64, device=dev)
+    bufs = torch.zeros(2, world, rows, k, dtype=torch.bfloat16, device=dev)          # [set][rank]
+    peer_x = [torch.tensor([bufs[s, r].data_ptr() for r in range(world)], dtype=torch.int64, device=dev) for s in range(2)]
+    gamma = synth_gamma(k, 2)
+    gamma_d = gamma.cuda()
+    res = [synth_activation(rows, k, seed=900 + s) for s in range(2)]
+    res_d = [r.cuda() for r in res]
+    h = [torch.empty(rows, k, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    p = [ops.alloc_packed(rows, k, k_hi, "rowmajor", dev) for _ in range(2)]
+    status = ops.status_word(dev)
+    status.zero_()
+
+    def call(s, stream):
+        st = _lib.lib().plq_allreduce_add_rmsnorm_pack(
+            peer_x[s].data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, s,
+            res_d[s].data_ptr(), h[s].data_ptr(), gamma_d.data_ptr(), 1e-6, rows, k, k_hi, 1, p[s].lo_codes.data_ptr(),
+            p[s].lo_sf.data_ptr(), p[s].hi_codes.data_ptr(), p[s].hi_sf.data_ptr(), p[s].sf_layout, status.data_ptr(),
+            stream.cuda_stream)
+        assert st == 0
+
+    def check(s, parts):
+        acc = np.zeros((rows, k), dtype=np.float32)
+        for part in parts:
+            acc = acc + f32_of(part)
+        want_h = F.add_bf16(f32_of(res[s]), F.round_to_bf16(acc))
+        assert np.array_equal(f32_of(h[s]), want_h)
+        want = F.prepare_activation(want_h, k_hi, gamma=f32_of(gamma), eps=1e-6, hadamard=True)
+        got = packed_to_numpy(p[s])
+        for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
+            assert np.array_equal(got[key], want[key]), key
+
+    side = torch.cuda.Stream(device=dev)
+    even = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(even, stream=side):
+            call(0, side)
+            call(1, side)
+    torch.cuda.synchronize()
+    for replay in range(1, 4):
+        parts = [[synth_activation(rows, k, seed=1000 * replay + 10 * s + r) for r in range(world)] for s in range(2)]
+        for s in range(2):
+            for r in range(world):
+                bufs[s, r].copy_(parts[s][r])
+        flags[1] = 2 * replay                                  # "rank 1 has announced both calls of this replay"
+        torch.cuda.synchronize()
+        even.replay()
+        plq.check_device_status(dev)
+        assert int(sync[0].item()) == 2 * replay
+        check(0, parts[0])
+        check(1, parts[1])
+
+    odd = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(odd, stream=side):
+            call(0, side)                                       # call 7 reads set 0: right the first time
+    torch.cuda.synchronize()
+    flags[1] = 8
+    odd.replay()
+    plq.check_device_status(dev)
+    odd.replay()                                                # call 8 must read set 1 but the graph names set 0
+    with pytest.raises(plq.PlqError) as e:
+        plq.check_device_status(dev)
+    assert e.value.status == 2
