@@ -706,6 +706,18 @@ def main_case(args):
         x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
         return x.to(torch.bfloat16).to(dev)
     name, k, n, _ = next(s for s in SHAPES if s[0] == args.shape)
+    if args.case == "decode_step":
+        # two layers of the Llama-3-70B-architecture stack on one GPU, batch 16, 2048 prefill tokens, a few decode
+        # steps (two eager, the rest replayed from the captured graph): the launch list of one step under profiles/
+        from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+        model = ResQForwardB200(LlamaConfig.llama3_70b(), dev, seed=4, num_layers=2)
+        ids = torch.randint(0, 128256, (16, 2048), generator=g).to(dev)
+        out = model.generate(ids, max(args.steps, 3))
+        torch.cuda.synchronize()
+        tev = model.timing_events
+        print(json.dumps({"case": "decode_step", "layers": 2, "decode_steps": int(out.shape[1]),
+                          "prefill_ms": tev[0].elapsed_time(tev[1]), "decode_ms": tev[1].elapsed_time(tev[2])}), flush=True)
+        return
     if args.case == "pack":
         x = activ(4096, 4096)
         gamma = (torch.rand(4096, generator=g) + 0.5).to(torch.bfloat16).to(dev)
@@ -757,7 +769,7 @@ def main_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["pack", "silu_pack", "gemv", "gemv_tc", "gemm"],
+    ap.add_argument("--case", default=None, choices=["pack", "silu_pack", "gemv", "gemv_tc", "gemm", "decode_step"],
                     help="run one kernel on one fixed case instead of the full step")
     ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
     ap.add_argument("--m", type=int, default=None)

@@ -58,7 +58,8 @@ struct PackArgs {
   int sf_tiled;
   int lo_chunks, hi_chunks;  // chunks per 128-row group in the tiled layouts
   int lanes;                 // threads per row: ceil(k / 64) rounded up to a whole warp
-  int rows_per_cta;
+  int rows_per_cta;          // with a row norm: rows per CTA (warps per CTA = rows_per_cta * lanes / 32)
+  int ngroups;               // groups of (warps per CTA) work units = ceil(rows * (lanes / 32) / warps per CTA)
   int stages;                // groups of rows in flight per CTA (1..3 shared-memory stages)
 };
 
@@ -183,8 +184,8 @@ __device__ __forceinline__ void read_line(const uint8_t* seg, int lane, uint32_t
 // read from the peers' memory: the all-reduce after a row-parallel linear, the residual add, the norm and the
 // quantiser of the next linear in one kernel.
 //
-// Persistent: a CTA of rows_per_cta x (lanes / 32) warps walks over groups of rows with a grid stride.  While a
-// group is computed from registers, the next group's segments are already on their way into shared memory.
+// Persistent: a CTA walks over groups of work units (one row segment per warp) with a grid stride.  While a
+// group is computed from registers, the next groups' segments are already on their way into shared memory.
 #ifdef PLQ_PACK_MAXNREG
 #define PLQ_PACK_BOUNDS __maxnreg__(PLQ_PACK_MAXNREG)
 #else
@@ -204,31 +205,38 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
   const int warp = tid >> 5;
   const int nwarps = blockDim.x >> 5;
   const int wpr = a.lanes >> 5;                     // warps (segments) per row
-  const int rl = warp / wpr;                        // which of the CTA's rows
-  const int seg = warp - rl * wpr;                  // which 2048-element segment of the row
-  const int l = 32 * seg + lane;                    // lane of the row: elements [64 l, 64 l + 64)
-  const int p = l & 1;
+  // Work unit = one segment of one row; unit u = row * wpr + segment.  Group g of a CTA with W warps holds units
+  // [g W, g W + W), one per warp.  Kernels with a row norm get W = rows_per_cta * wpr from the launcher, so that the
+  // warps of a row share a CTA and warp w always has segment w % wpr of the CTA's row w / wpr; the others may cut
+  // rows anywhere (a decode batch of 16 long rows still fills the GPU).
+  const int rl = warp / wpr;                        // with a row norm: which of the CTA's rows
+  const int p = lane & 1;
   const int flip = HAD ? p : 0;                     // odd lanes of a rotated row hold their runs swapped
-  const int in0 = 64 * l + 32 * flip;               // first element of register run 0 / run 1 as loaded
-  const int in1 = 64 * l + 32 - 32 * flip;
   const int k8 = a.k >> 3;
   const uint32_t xr = static_cast<uint32_t>((lane & 7) ^ (4 * flip)) << 4;   // chunk swizzle of this lane's line, run 0 first
-  const int seg_pieces = min(max(k8 - 256 * seg, 0), 256);        // 16-byte pieces of this segment inside the row
+  struct Unit { int row, seg; };
+  auto unit_of = [&](int group) {
+    const int u = group * nwarps + warp;
+    Unit t;
+    t.row = u / wpr;
+    t.seg = u - t.row * wpr;
+    return t;
+  };
   constexpr bool kStageX = PRO != 3;                // prologue 3 reads x from the peers, straight into registers
   constexpr bool kStageX2 = PRO != 0;
   constexpr int kOperands = (kStageX ? 1 : 0) + (kStageX2 ? 1 : 0);
   const int stage_bytes = kOperands * nwarps * kSegBytes;           // one group of rows, all staged operands
   uint8_t* xs0 = pack_smem + warp * kSegBytes;                       // stage 0; stage s is s * stage_bytes further
   uint8_t* x2s0 = pack_smem + ((kStageX ? nwarps : 0) + warp) * kSegBytes;
-  uint8_t* gs = pack_smem + a.stages * stage_bytes + seg * 2 * kSegBytes;   // gamma as float32: shared by the rows
+  uint8_t* gs = pack_smem + a.stages * stage_bytes + (warp - rl * wpr) * 2 * kSegBytes;   // gamma as float32, this warp's segment
   const int ld2 = PRO == 1 ? a.ldx8 : k8;           // row stride of x2 in 16-byte units
 
   auto stage_group = [&](int group, int slot) {
-    const int row = group * a.rows_per_cta + rl;
-    const int n = row < a.rows ? seg_pieces : 0;
-    const size_t r0 = static_cast<size_t>(row < a.rows ? row : 0);
-    if constexpr (kStageX) stage_segment(smem_u32(xs0 + slot * stage_bytes), a.x + r0 * a.ldx8 + 256 * seg, n, lane);
-    if constexpr (kStageX2) stage_segment(smem_u32(x2s0 + slot * stage_bytes), a.x2 + r0 * ld2 + 256 * seg, n, lane);
+    const Unit t = unit_of(group);
+    const int n = t.row < a.rows ? min(max(k8 - 256 * t.seg, 0), 256) : 0;     // 16-byte pieces of the segment inside the row
+    const size_t r0 = static_cast<size_t>(t.row < a.rows ? t.row : 0);
+    if constexpr (kStageX) stage_segment(smem_u32(xs0 + slot * stage_bytes), a.x + r0 * a.ldx8 + 256 * t.seg, n, lane);
+    if constexpr (kStageX2) stage_segment(smem_u32(x2s0 + slot * stage_bytes), a.x2 + r0 * ld2 + 256 * t.seg, n, lane);
   };
 
   if constexpr (PRO == 3) {
@@ -260,15 +268,16 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     __syncthreads();
   }
 
-  const int ngroups = (a.rows + a.rows_per_cta - 1) / a.rows_per_cta;
+  const int ngroups = a.ngroups;
   int group = blockIdx.x;
   if constexpr (NORM) {
     // The norm weights, widened to float32 once per CTA: lane `lane` of segment `seg` finds its 64 values, in its
     // own register order, as sixteen 16-byte pieces at gs + (16 c + ...): piece c of all 32 lanes is contiguous.
     if (rl == 0) {
+      const int gl = 32 * (warp - rl * wpr) + lane;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const int e = (c < 4 ? in0 : in1) + 8 * (c & 3);
+        const int e = 64 * gl + (c < 4 ? 32 * flip : 32 - 32 * flip) + 8 * (c & 3);
         const uint4 gq = e < a.k ? __ldg(a.gamma + (e >> 3)) : make_uint4(0, 0, 0, 0);
         float2 g[4];
         unpack8(gq, g);
@@ -286,7 +295,11 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
   int iter = 0, slot = 0;
 
   for (; group < ngroups; group += stride, ++iter) {
-    const int row = group * a.rows_per_cta + rl;
+    const Unit unit = unit_of(group);
+    const int row = unit.row;
+    const int l = 32 * unit.seg + lane;               // lane of the row: elements [64 l, 64 l + 64)
+    const int in0 = 64 * l + 32 * flip;               // first element of register run 0 / run 1 as loaded
+    const int in1 = 64 * l + 32 - 32 * flip;
     const bool row_ok = row < a.rows;
     const bool ok0 = row_ok && in0 < a.k, ok1 = row_ok && in1 < a.k;
     // v[16 r + 4 c + i] holds elements (8 c + 2 i, 8 c + 2 i + 1) of register run r.  Arithmetic on pairs uses the
@@ -647,16 +660,29 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.sf_tiled = sf_layout == PLQ_SF_TILED;
   a.lo_chunks = static_cast<int>(((k - k_hi) / 16 + 3) / 4);
   a.hi_chunks = static_cast<int>((k_hi / 32 + 3) / 4);
-  // threads per row: one per 64 elements, whole warps; rows per CTA: as many as fit the target CTA size, fewer
-  // when the groups of rows would not cover the GPU a few times over (decode batches)
+  // threads per row: one per 64 elements, whole warps.  With a row norm a CTA holds whole rows: as many as fit the
+  // target CTA size, fewer when the groups would not cover the GPU a few times over (decode batches).  Without one
+  // the unit of work is a row segment (one warp) and a CTA takes any `warps` of them.
   const int lanes = ((static_cast<int>((k + 63) / 64) + 31) / 32) * 32;
-  int rpc = kPackTargetThreads / lanes;
-  if (rpc < 1) rpc = 1;
-  if (rpc > 8) rpc = 8;                               // one named barrier per row of the CTA
-  while (rpc > 1 && (rows + rpc - 1) / rpc < 4 * static_cast<int64_t>(sm_count())) rpc >>= 1;
+  const int wpr = lanes / 32;
+  const int64_t units = rows * wpr;
+  int warps;
+  if (norm) {
+    int rpc = kPackTargetThreads / lanes;
+    if (rpc < 1) rpc = 1;
+    if (rpc > 8) rpc = 8;                               // one named barrier per row of the CTA
+    while (rpc > 1 && (rows + rpc - 1) / rpc < 4 * static_cast<int64_t>(sm_count())) rpc >>= 1;
+    a.rows_per_cta = rpc;
+    warps = rpc * wpr;
+  } else {
+    warps = kPackTargetThreads / 32;
+    while (warps > 1 && (units + warps - 1) / warps < 4 * static_cast<int64_t>(sm_count())) warps >>= 1;
+    a.rows_per_cta = 0;
+  }
   a.lanes = lanes;
-  a.rows_per_cta = rpc;
-  const int threads = lanes * rpc;
+  const int threads = 32 * warps;
+  const int64_t groups = (units + warps - 1) / warps;
+  a.ngroups = static_cast<int>(groups);
   // shared memory: `stages` groups of rows in flight (each: the staged operands of all warps) + gamma.  Kernels
   // that do little arithmetic per byte (no norm) need more bytes in flight to cover the HBM latency.
   const int stage_bytes = ((pro != 3) + (pro != 0)) * (threads / 32) * kSegBytes;
@@ -665,7 +691,6 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   while (stages > 1 && 4 * (stages * stage_bytes + gamma_bytes) > 216 * 1024) --stages;   // keep four CTAs per SM
   a.stages = stages;
   const int smem = stages * stage_bytes + gamma_bytes;
-  const int64_t groups = (rows + rpc - 1) / rpc;
   auto launch = [&](void (*kernel)(const PackArgs)) -> int {
     int per_sm = 0;
     const int st = resident_ctas(reinterpret_cast<const void*>(kernel), threads, smem, &per_sm);

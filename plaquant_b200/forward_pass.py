@@ -19,8 +19,9 @@ Weights are random-initialised per layer from a seed (no checkpoints are availab
 from __future__ import annotations
 
 import math
+import re
 from dataclasses import dataclass
-from typing import List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -78,7 +79,12 @@ class ResQForwardB200:
     """Decoder stack with packed weights resident on one GPU (one tensor-parallel rank)."""
 
     def __init__(self, cfg: LlamaConfig, device, ctx: Optional[tp.TPContext] = None, seed: int = 0,
-                 num_layers: Optional[int] = None, fused_reduce_rows: int = 0, kv_quant: bool = False):
+                 num_layers: Optional[int] = None, fused_reduce_rows: int = 0, kv_quant: bool = False,
+                 weights: Optional[Dict[str, torch.Tensor]] = None, packed: Optional[dict] = None):
+        """Weights come from one of three places: `packed` (the state a packed-weight container holds, see
+        weight_packer.py), `weights` (a dict of full bf16 tensors under the reference's names, `l{i}.q_proj.weight`
+        ... as `IndependentResQForward` takes them; every rank picks its own shard), or, with neither, a random
+        initialisation per layer from `seed` (no checkpoints are available offline)."""
         self.cfg, self.device, self.ctx = cfg, torch.device(device), ctx or tp.TPContext()
         c, r, s = cfg, self.ctx.rank, self.ctx.size
         assert c.num_heads % s == 0 and c.num_kv_heads % s == 0 and c.intermediate_size % (s * 128) == 0
@@ -89,37 +95,124 @@ class ResQForwardB200:
         self.k_hi_ffn = tp.outlier_count(self.ffn, c.high_fraction)                     # rank-local K of down_proj
         self.layers: List[_Layer] = []
         n_layers = c.num_layers if num_layers is None else num_layers
-        for li in range(n_layers):
-            g = torch.Generator(device=self.device).manual_seed(seed * 100003 + li * 16 + r)
-            L = _Layer()
-            L.ln1 = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
-            L.ln2 = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
-            L.qkv = self._linear((self.heads + 2 * self.kv_heads) * c.head_dim, c.hidden_size, self.k_hi_hidden, g)
-            L.o = self._linear(c.hidden_size, self.heads * c.head_dim, self.k_hi_attn, g)
-            L.gate_up = self._linear(2 * self.ffn, c.hidden_size, self.k_hi_hidden, g)
-            L.down = self._linear(c.hidden_size, self.ffn, self.k_hi_ffn, g)
-            self.layers.append(L)
-        g = torch.Generator(device=self.device).manual_seed(seed * 100003 + 999983)      # replicated on every rank
-        self.embed = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
-        self.final_norm = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
-        self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+        if packed is not None:
+            self._load_packed(packed, n_layers)
+        else:
+            for li in range(n_layers):
+                t = self._shard_of(weights, li) if weights is not None else self._random_layer(li, seed)
+                L = _Layer()
+                L.ln1, L.ln2 = t["ln1"], t["ln2"]
+                L.qkv = self._linear(t.pop("qkv"), self.k_hi_hidden)
+                L.o = self._linear(t.pop("o"), self.k_hi_attn)
+                L.gate_up = self._linear(t.pop("gate_up"), self.k_hi_hidden)
+                L.down = self._linear(t.pop("down"), self.k_hi_ffn)
+                self.layers.append(L)
+            if weights is not None:
+                to = dict(device=self.device, dtype=torch.bfloat16)
+                self.embed, self.final_norm = weights["embed"].to(**to), weights["final_norm"].to(**to)
+                self.lm_head = weights["lm_head"].to(**to)
+            else:
+                g = torch.Generator(device=self.device).manual_seed(seed * 100003 + 999983)      # replicated on every rank
+                self.embed = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+                self.final_norm = (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)
+                self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
         self.kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
         self.pos = 0
         # keys go into the cache as NVFP4 (Hadamard over the head dimension, per-head rows), queries get the same
         # rotation: the reference's QKRotationWrapper with k_had (promix/quantize/kv_quant.py:244-279)
-        self.kv_quant = kv_quant
+        self.kv_quant = kv_quant                     # False | True (packed NVFP4 rows in the cache) | "fake" (their bf16 values)
         if kv_quant and c.head_dim != 128:
             raise ValueError("kv_quant needs head_dim = 128 (one Hadamard block per head)")
         # decode batches of up to `fused_reduce_rows` rows reduce over peer memory inside the RMSNorm-quant kernel
         self.peer = (tp.PeerReduce(fused_reduce_rows, c.hidden_size, self.device, self.ctx.group)
                      if fused_reduce_rows > 0 and self.ctx.size > 1 else None)
 
-    def _linear(self, n: int, k: int, k_hi: int, g: torch.Generator) -> QuantizedLinear:
-        """Random N(0, 0.02) weight [n, k], rotated and packed on the device; only the packed form is kept."""
-        w = (torch.randn(n, k, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+    # ---- where the weights come from ---------------------------------------------------------------
+    def _random_layer(self, li: int, seed: int) -> Dict[str, torch.Tensor]:
+        """This rank's bf16 tensors of layer `li`: norm weights ~ U(0.5, 1.5), linears ~ N(0, 0.02)."""
+        c, r = self.cfg, self.ctx.rank
+        g = torch.Generator(device=self.device).manual_seed(seed * 100003 + li * 16 + r)
+
+        def lin(n, k):
+            return (torch.randn(n, k, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
+        t = {"ln1": (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16),
+             "ln2": (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)}
+        t["qkv"] = lin((self.heads + 2 * self.kv_heads) * c.head_dim, c.hidden_size)
+        t["o"] = lin(c.hidden_size, self.heads * c.head_dim)
+        t["gate_up"] = lin(2 * self.ffn, c.hidden_size)
+        t["down"] = lin(c.hidden_size, self.ffn)
+        return t
+
+    def _shard_of(self, weights: Dict[str, torch.Tensor], li: int) -> Dict[str, torch.Tensor]:
+        """This rank's tensors of layer `li` cut out of full weights under the reference's names
+        (inference/forward_pass.py:185-276 there): column-parallel q/k/v (by heads) and gate/up (by FFN columns),
+        fused into one [q | k | v] and one [gate | up] matrix; row-parallel o_proj (input columns of this rank's
+        heads) and down_proj (input columns of this rank's FFN slice)."""
+        c, r, s, p = self.cfg, self.ctx.rank, self.ctx.size, f"l{li}"
+        to = dict(device=self.device, dtype=torch.bfloat16)
+        hd = c.head_dim
+        qs = tp.column_parallel_rows(c.num_heads * hd, r, s)
+        ks = tp.column_parallel_rows(c.num_kv_heads * hd, r, s)
+        fs = tp.column_parallel_rows(c.intermediate_size, r, s)
+        oc = tp.row_parallel_cols(c.num_heads * hd, r, s)
+        dc = tp.row_parallel_cols(c.intermediate_size, r, s)
+        w = lambda name: weights[f"{p}.{name}.weight"]
+        return {
+            "ln1": weights[f"{p}.ln1"].to(**to), "ln2": weights[f"{p}.ln2"].to(**to),
+            "qkv": torch.cat([w("q_proj")[qs], w("k_proj")[ks], w("v_proj")[ks]], 0).to(**to),
+            "o": w("o_proj")[:, oc].to(**to).contiguous(),
+            "gate_up": torch.cat([w("mlp.gate_proj")[fs], w("mlp.up_proj")[fs]], 0).to(**to),
+            "down": w("mlp.down_proj")[:, dc].to(**to).contiguous(),
+        }
+
+    def _linear(self, w: torch.Tensor, k_hi: int) -> QuantizedLinear:
+        """bf16 weight [n, k] -> rotated and packed on the device; only the packed form is kept."""
         p = ops.pack(w, k_hi, hadamard=True, sf_layout="rowmajor")
-        del w
         return QuantizedLinear(p.lo_codes, p.lo_sf, p.hi_codes, p.hi_sf, online_had=True)
+
+    def packed_state(self) -> dict:
+        """Everything needed to rebuild this rank's model without the bf16 weights: per linear the packed codes
+        and row-major scale bytes, the norm weights, embedding and LM head (see weight_packer.save_packed)."""
+        c = self.cfg
+        tensors, linears = {"embed": self.embed, "final_norm": self.final_norm, "lm_head": self.lm_head}, {}
+        for li, L in enumerate(self.layers):
+            tensors[f"l{li}.ln1"], tensors[f"l{li}.ln2"] = L.ln1, L.ln2
+            for name in ("qkv", "o", "gate_up", "down"):
+                q: QuantizedLinear = getattr(L, name)
+                key = f"l{li}.{name}"
+                tensors[key + ".lo_codes"], tensors[key + ".lo_sf"] = q.w_main_int, q.w_main_scale
+                tensors[key + ".hi_codes"], tensors[key + ".hi_sf"] = q.w_high_int, q.w_high_scale
+                linears[key] = {"n": q.out_features, "k_lo": q.w_main_int.shape[1] * 2, "k_hi": q.high_bits_length,
+                                "rotated": True, "sf_layout": "rowmajor"}
+        return {"config": dict(vars(c)), "num_layers": len(self.layers), "tp": {"rank": self.ctx.rank, "size": self.ctx.size},
+                "tensors": tensors, "linears": linears}
+
+    def _load_packed(self, state: dict, n_layers: int) -> None:
+        if (state["tp"]["rank"], state["tp"]["size"]) != (self.ctx.rank, self.ctx.size):
+            raise ValueError(f"packed weights were written for rank {state['tp']['rank']} of {state['tp']['size']}, "
+                             f"this is rank {self.ctx.rank} of {self.ctx.size}: the K split of the row-parallel linears "
+                             "(each rank's own MXFP8 columns) depends on the tensor-parallel degree")
+        if n_layers > state["num_layers"]:
+            raise ValueError(f"the container holds {state['num_layers']} layers, {n_layers} were asked for")
+        def wanted(name: str) -> bool:               # "l{i}.*" of the layers kept, and the tensors outside the layers
+            m = re.match(r"l(\d+)\.", name)
+            return m is None or int(m.group(1)) < n_layers
+        t = {k: v.to(self.device) for k, v in state["tensors"].items() if wanted(k)}
+        for li in range(n_layers):
+            L = _Layer()
+            L.ln1, L.ln2 = t[f"l{li}.ln1"], t[f"l{li}.ln2"]
+            for name in ("qkv", "o", "gate_up", "down"):
+                key = f"l{li}.{name}"
+                meta = state["linears"][key]
+                if not meta["rotated"] or meta["sf_layout"] != "rowmajor":
+                    raise ValueError(f"{key}: unsupported container entry {meta}")
+                q = QuantizedLinear(t[key + ".lo_codes"], t[key + ".lo_sf"], t[key + ".hi_codes"], t[key + ".hi_sf"],
+                                    online_had=True)
+                if (q.out_features, q.in_features - q.high_bits_length, q.high_bits_length) != (meta["n"], meta["k_lo"], meta["k_hi"]):
+                    raise ValueError(f"{key}: tensor shapes do not match the recorded {meta}")
+                setattr(L, name, q)
+            self.layers.append(L)
+        self.embed, self.final_norm, self.lm_head = t["embed"], t["final_norm"], t["lm_head"]
 
     # ---- pieces ----------------------------------------------------------------------------------
     def _quantized_linear(self, x, lin: QuantizedLinear, norm_weight=None):
@@ -169,20 +262,31 @@ class ResQForwardB200:
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
         q, k = self._rope(q, k, cos_sin)
         if self.kv_quant:
+            # NVFP4 cache: keys rotated over the head dimension (queries get the same rotation), values as they are
+            # (the reference's k_bits / v_bits "nvfp4", promix/configs/llama-3-8b-mxfp8-nvfp4-kv4.yaml:20-25).  The
+            # cache holds the packed rows: 64 code bytes + 8 scale bytes per (token, head) instead of 256 bytes.
             q = kv_cache.rotate_heads(q)
-            k = kv_cache.dequantize_heads(kv_cache.quantize_heads(k.contiguous()), k.shape)   # what the packed cache holds
+            k = kv_cache.pack_head_rows(k, hadamard=True)
+            v = kv_cache.pack_head_rows(v, hadamard=False)
+            if self.kv_quant == "fake":            # keep, in bf16, exactly what the packed cache gives back
+                k, v = kv_cache.unpack_head_rows(k), kv_cache.unpack_head_rows(v)
+        packed_cache = bool(self.kv_quant) and self.kv_quant != "fake"
         if static is None:
             if pos0 == 0:
                 self.kv[li] = (k, v)
             else:
                 self.kv[li] = (torch.cat([self.kv[li][0], k], 1), torch.cat([self.kv[li][1], v], 1))
             kk, vv = self.kv[li]
+            if packed_cache:                       # dequantise on read (no attention kernel reads the codes yet)
+                kk, vv = kv_cache.unpack_head_rows(kk), kv_cache.unpack_head_rows(vv)
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   is_causal=(t > 1), enable_gqa=True)
         else:
             kk, vv = static["k"][li], static["v"][li]
             kk.index_copy_(1, static["pos"], k)
             vv.index_copy_(1, static["pos"], v)
+            if packed_cache:
+                kk, vv = kv_cache.unpack_head_rows(kk), kv_cache.unpack_head_rows(vv)
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   attn_mask=static["mask"], enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
@@ -211,8 +315,9 @@ class ResQForwardB200:
 
     # ---- public ----------------------------------------------------------------------------------
     @torch.no_grad()
-    def forward(self, input_ids: torch.Tensor, pos0: int = 0) -> torch.Tensor:
-        """input_ids [B, T] -> logits of the last position [B, vocab] (float32)."""
+    def forward(self, input_ids: torch.Tensor, pos0: int = 0, all_positions: bool = False) -> torch.Tensor:
+        """input_ids [B, T] -> logits of the last position [B, vocab] (float32), or of every position
+        [B, T, vocab] with `all_positions` (what the reference's forward returns, forward_pass.py:178-183)."""
         if pos0 == 0:
             self.kv = [None] * len(self.layers)
         h = F.embedding(input_ids, self.embed)
@@ -222,10 +327,11 @@ class ResQForwardB200:
         for li in range(len(self.layers)):
             h, delta = self._forward_layer(li, h, delta, pos0, cos_sin)
         self.pos = pos0 + input_ids.shape[1]
-        return self._logits(self._finish(h, delta)[:, -1])
+        h = self._finish(h, delta)
+        return self._logits(h if all_positions else h[:, -1])
 
     def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
-        """Final norm + unquantised LM head in the model dtype (inference/forward_pass.py:178-181 in the reference)."""
+        """Final norm + unquantised LM head in the model dtype, for rows [..., hidden] (inference/forward_pass.py:178-181 in the reference)."""
         last = rms_norm(h_last, self.final_norm, self.cfg.rms_eps)
         return F.linear(last, self.lm_head).float()
 
@@ -255,7 +361,7 @@ class ResQForwardB200:
               "mask": torch.zeros(1, 1, 1, t_max, dtype=torch.bool, device=dev)}
         for li in range(len(self.layers)):
             for name, src in (("k", self.kv[li][0]), ("v", self.kv[li][1])):
-                buf = torch.zeros(b, t_max, self.kv_heads, c.head_dim, dtype=src.dtype, device=dev)
+                buf = torch.zeros(b, t_max, self.kv_heads, src.shape[-1], dtype=src.dtype, device=dev)   # bf16 rows or packed rows
                 buf[:, :t0] = src
                 st[name].append(buf)
         self.kv = [None] * len(self.layers)
@@ -304,3 +410,103 @@ class ResQForwardB200:
         self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. capture) = ev[1] -> ev[2], once synchronised
         self.pos = t_max
         return out
+
+
+class IndependentResQForward:
+    """The reference's forward object by name (inference/forward_pass.py:118-183 there): built from a dict of
+    weights and a config dict, moved to the GPU with `.to()`, `forward(input_ids)` returns the logits of every
+    position.  Here the linears run on the packed NVFP4 / MXFP8 kernels; the object is a thin shell around
+    `ResQForwardB200`.
+
+    weights  {"embed", "final_norm", "lm_head", "l{i}.ln1", "l{i}.ln2", "l{i}.q_proj.weight", "l{i}.k_proj.weight",
+             "l{i}.v_proj.weight", "l{i}.o_proj.weight", "l{i}.mlp.gate_proj.weight", "l{i}.mlp.up_proj.weight",
+             "l{i}.mlp.down_proj.weight"}: full (unsharded) tensors, any float dtype; quantised on the device when
+             the object is moved there (round to nearest; last 1/32 of the input channels in MXFP8).
+    config   {"num_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "intermediate_size",
+             "rope_theta", optional "vocab_size", "rms_eps", "high_fraction"}
+
+    Differences from the reference that follow from the formats: every linear rotates its input by the
+    block-Hadamard(128) (the weights carry the same rotation, applied once at packing time), so `online_had` of
+    `_quantized_linear` has nothing left to switch; q/k/v and gate/up are stored fused."""
+
+    def __init__(self, weights: Dict[str, torch.Tensor], config: dict, ctx: Optional[tp.TPContext] = None, **model_kw):
+        self.weights, self.config, self.ctx, self._model_kw = weights, config, ctx, model_kw
+        self.num_layers = config["num_layers"]
+        self.hidden_size = config["hidden_size"]
+        self.num_heads = config["num_attention_heads"]
+        self.num_kv_heads = config["num_key_value_heads"]
+        self.head_dim = self.hidden_size // self.num_heads
+        self.intermediate_size = config["intermediate_size"]
+        self.rope_theta = config.get("rope_theta", 500000.0)
+        self.device = "cpu"
+        self.model: Optional[ResQForwardB200] = None
+
+    def _llama_config(self) -> LlamaConfig:
+        c = self.config
+        return LlamaConfig(self.hidden_size, self.intermediate_size, self.num_layers, self.num_heads, self.num_kv_heads,
+                           self.head_dim, c.get("vocab_size", self.weights["embed"].shape[0]), self.rope_theta,
+                           c.get("rms_eps", 1e-5), c.get("high_fraction", 1.0 / 32))
+
+    def to(self, device):
+        """Moves to `device` (a CUDA device: there is no CPU path) and packs the weights there."""
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("IndependentResQForward runs on a CUDA device only: plaquant_b200 has no CPU path")
+        self.device = device
+        self.model = ResQForwardB200(self._llama_config(), dev, self.ctx, weights=self.weights, **self._model_kw)
+        return self
+
+    def _require_model(self) -> ResQForwardB200:
+        if self.model is None:
+            raise RuntimeError("call .to('cuda') first: the weights are packed on the device")
+        return self.model
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Full forward pass; logits [B, T, vocab] (float32)."""
+        return self._require_model().forward(input_ids, all_positions=True)
+
+    __call__ = forward
+
+    def generate(self, input_ids: torch.Tensor, steps: int, **kw) -> torch.Tensor:
+        return self._require_model().generate(input_ids, steps, **kw)
+
+    _SLICES = {"q_proj": ("qkv", 0), "k_proj": ("qkv", 1), "v_proj": ("qkv", 2), "o_proj": ("o", None),
+               "mlp.gate_proj": ("gate_up", 0), "mlp.up_proj": ("gate_up", 1), "mlp.down_proj": ("down", None)}
+
+    def _quantized_linear(self, x: torch.Tensor, prefix: str, online_had: bool = False) -> torch.Tensor:
+        """x[..., K] through the quantised linear named `prefix` ("l3.q_proj", "l0.mlp.down_proj", ...), as
+        forward_pass.py:278-319 of the reference: rotation, activation quantiser, packed product (this rank's
+        shard under tensor parallelism).  q/k/v and gate/up are slices of their fused linears."""
+        m = self._require_model()
+        layer, name = prefix.split(".", 1)
+        fused, part = self._SLICES[name]
+        y = m._quantized_linear(x, getattr(m.layers[int(layer[1:])], fused))
+        if part is None:
+            return y
+        hd = m.cfg.head_dim
+        sizes = [m.heads * hd, m.kv_heads * hd, m.kv_heads * hd] if fused == "qkv" else [m.ffn, m.ffn]
+        return y.split(sizes, -1)[part]
+
+
+def synthetic_weights(cfg: LlamaConfig, seed: int = 0, num_layers: Optional[int] = None, device="cuda") -> Dict[str, torch.Tensor]:
+    """The weights `ResQForwardB200(cfg, device, seed=seed)` draws on one rank, as a dict under the reference's
+    names (the form `IndependentResQForward` takes).  Only sensible for small configurations: the dict holds
+    every bf16 tensor at once."""
+    probe = ResQForwardB200.__new__(ResQForwardB200)
+    probe.cfg, probe.device, probe.ctx = cfg, torch.device(device), tp.TPContext()
+    probe.heads, probe.kv_heads, probe.ffn = cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size
+    hd = cfg.head_dim
+    out: Dict[str, torch.Tensor] = {}
+    for li in range(cfg.num_layers if num_layers is None else num_layers):
+        t = probe._random_layer(li, seed)
+        q, k, v = t["qkv"].split([cfg.num_heads * hd, cfg.num_kv_heads * hd, cfg.num_kv_heads * hd], 0)
+        gate, up = t["gate_up"].split([cfg.intermediate_size, cfg.intermediate_size], 0)
+        p = f"l{li}"
+        out.update({f"{p}.ln1": t["ln1"], f"{p}.ln2": t["ln2"], f"{p}.q_proj.weight": q, f"{p}.k_proj.weight": k,
+                    f"{p}.v_proj.weight": v, f"{p}.o_proj.weight": t["o"], f"{p}.mlp.gate_proj.weight": gate,
+                    f"{p}.mlp.up_proj.weight": up, f"{p}.mlp.down_proj.weight": t["down"]})
+    g = torch.Generator(device=probe.device).manual_seed(seed * 100003 + 999983)
+    out["embed"] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g, device=probe.device) * 0.02).to(torch.bfloat16)
+    out["final_norm"] = (torch.rand(cfg.hidden_size, generator=g, device=probe.device) + 0.5).to(torch.bfloat16)
+    out["lm_head"] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g, device=probe.device) * 0.02).to(torch.bfloat16)
+    return out

@@ -45,3 +45,28 @@ def rotate_heads(q: torch.Tensor) -> torch.Tensor:
     if h is None:                      # built once per device: no host-to-device copy inside a CUDA-graph capture
         h = _H[key] = get_hadamard_matrix(q.shape[-1]).to(device=q.device, dtype=torch.float32)
     return (q.float() @ h).to(q.dtype)
+
+
+HEAD_DIM = 128
+ROW_BYTES = HEAD_DIM // 2 + HEAD_DIM // 16      # 64 bytes of E2M1 codes + 8 E4M3 scale bytes per (token, head)
+
+
+def pack_head_rows(x: torch.Tensor, hadamard: bool) -> torch.Tensor:
+    """x: bf16 [..., heads, 128] -> uint8 [..., heads, 72]: the cache's storage form, per (token, head) the 64
+    code bytes of the NVFP4 row followed by its 8 scale bytes (keys: `hadamard=True`, the rotation over the head
+    dimension; values: False).  0.5625 byte per element instead of 2."""
+    if x.shape[-1] != HEAD_DIM:
+        raise ValueError("the packed key/value cache needs head_dim = 128")
+    p = quantize_heads(x.contiguous(), 0, hadamard=hadamard)
+    return torch.cat([p.lo_codes, p.lo_sf], 1).view(*x.shape[:-1], ROW_BYTES)
+
+
+def unpack_head_rows(rows: torch.Tensor) -> torch.Tensor:
+    """uint8 [..., heads, 72] -> bf16 [..., heads, 128]: the values the reference's fake quantiser leaves in its
+    cache (keys still in the rotated basis).  All-zero rows (positions not written yet) give zeros."""
+    flat = rows.reshape(-1, ROW_BYTES)
+    n = flat.shape[0]
+    empty = torch.zeros(n, 0, dtype=torch.uint8, device=rows.device)
+    p = ops.PackedMatrix(n, HEAD_DIM, 0, flat[:, : HEAD_DIM // 2].contiguous(), flat[:, HEAD_DIM // 2:].contiguous(),
+                         empty, empty, ops.SF_ROWMAJOR)
+    return ops.unpack(p).view(*rows.shape[:-1], HEAD_DIM)

@@ -151,15 +151,72 @@ def test_kv_cache_quantisation_per_head(k_hi):
     assert rel_l2(s_q.cpu().numpy(), s_ref.cpu().numpy()) < 0.35       # 4-bit keys with x20 outlier channels
 
 
-def test_decoder_with_quantised_key_cache():
-    """kv_quant: rotated queries against NVFP4 keys give logits close to the bf16-key run, eager and graph decode agree."""
+def test_decoder_with_packed_nvfp4_key_value_cache():
+    """kv_quant: the cache holds packed NVFP4 rows (keys rotated, values plain).  The stored bytes equal the
+    oracle's for the same keys / values; logits and generated tokens equal, bit for bit, those of the run that
+    stores the dequantised bf16 values instead ("fake": the reference's semantics); both stay close to the run with
+    a bf16 cache; eager and graph decode agree."""
+    from plaquant_b200 import kv_cache
     from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+    kv = synth_activation(2 * 5 * 3, 128, seed=31).view(2, 5, 3, 128)
+    for had in (True, False):
+        rows = kv_cache.pack_head_rows(kv.cuda(), hadamard=had)
+        want = F.prepare_activation(f32_of(kv.view(-1, 128)), 0, hadamard=had)
+        assert rows.shape == (2, 5, 3, 72) and rows.dtype == torch.uint8
+        got = rows.view(-1, 72).cpu().numpy()
+        assert np.array_equal(got[:, :64], want["lo_codes"]) and np.array_equal(got[:, 64:], want["lo_sf"])
+        back = kv_cache.unpack_head_rows(rows)
+        assert np.array_equal(f32_of(back.view(-1, 128)), F.round_to_bf16(F.dequant_mixed(want)))
+    assert not kv_cache.unpack_head_rows(torch.zeros(1, 2, 1, 72, dtype=torch.uint8, device="cuda")).any()
     cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=128,
                       vocab_size=500)
     ids = torch.randint(0, 500, (2, 24), generator=torch.Generator().manual_seed(3)).cuda()
     ref = ResQForwardB200(cfg, "cuda", seed=2).forward(ids)
+    fake = ResQForwardB200(cfg, "cuda", seed=2, kv_quant="fake")
     model = ResQForwardB200(cfg, "cuda", seed=2, kv_quant=True)
     got = model.forward(ids)
+    assert model.kv[0][0].dtype == torch.uint8 and model.kv[0][0].shape == (2, 24, 1, 72)     # the cache is packed
+    assert torch.equal(got, fake.forward(ids))
     assert torch.isfinite(got).all() and rel_l2(got.cpu().numpy(), ref.cpu().numpy()) < 0.3
-    assert torch.equal(model.generate(ids, 4), model.generate(ids, 4, use_graph=False))
+    gen = model.generate(ids, 4)
+    assert torch.equal(gen, model.generate(ids, 4, use_graph=False)) and torch.equal(gen, fake.generate(ids, 4))
+    plq.check_device_status()
+
+
+def test_independent_resq_forward_from_a_weights_dict_matches_the_seeded_decoder(tmp_path):
+    """The reference-named forward object: built from {name: bf16 tensor} + a config dict, `.to("cuda")`, logits
+    for every position - bit-identical to ResQForwardB200 drawing the same weights from its seed; per-linear
+    access by the reference's prefixes; and the packed-weight container: save -> load gives identical logits."""
+    from plaquant_b200 import tp, weight_packer
+    from plaquant_b200.forward_pass import IndependentResQForward, LlamaConfig, ResQForwardB200, synthetic_weights
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      vocab_size=1000)
+    ids = torch.randint(0, 1000, (3, 24), generator=torch.Generator().manual_seed(0)).cuda()
+    seeded = ResQForwardB200(cfg, "cuda", seed=5)
+    want_last = seeded.forward(ids)
+    weights = {k: v.cpu() for k, v in synthetic_weights(cfg, seed=5).items()}
+    config = {"num_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+              "intermediate_size": 512, "rope_theta": cfg.rope_theta, "rms_eps": cfg.rms_eps}
+    fwd = IndependentResQForward(weights, config)
+    with pytest.raises(RuntimeError):
+        fwd.forward(ids)                                    # still on the CPU: there is no CPU path
+    fwd = fwd.to("cuda")
+    logits = fwd.forward(ids)
+    assert logits.shape == (3, 24, 1000) and logits.dtype == torch.float32
+    assert torch.equal(logits[:, -1], want_last)
+    assert torch.equal(seeded.forward(ids, all_positions=True), logits)
+    # per-linear entry point under the reference's prefixes: slices of the fused linears
+    x = synth_activation(5, 256, seed=9).cuda()
+    q = fwd._quantized_linear(x, "l1.q_proj")
+    k = fwd._quantized_linear(x, "l1.k_proj")
+    assert q.shape == (5, 256) and k.shape == (5, 128)
+    want_q = _oracle_linear(x, weights["l1.q_proj.weight"], fwd.model.k_hi_hidden)
+    assert rel_l2(f32_of(q), want_q) <= 1e-3
+    # container round trip
+    path = weight_packer.save_packed(seeded, str(tmp_path / "model.plq"))
+    loaded = weight_packer.load_packed(path, "cuda")
+    assert torch.equal(loaded.forward(ids), want_last)
+    assert torch.equal(loaded.generate(ids, 4), seeded.generate(ids, 4))
+    with pytest.raises(ValueError):
+        weight_packer.load_packed(path, "cuda", ctx=tp.TPContext(1, 2, None))   # written for one rank, not for rank 1 of 2
     plq.check_device_status()

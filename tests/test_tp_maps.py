@@ -112,3 +112,35 @@ def _failing_pair(q):
         q.put("unexpected-success")
     except Exception:
         q.put("timeout-detected")
+
+
+def test_shards_of_a_weights_dict_partition_the_model():
+    """`ResQForwardB200._shard_of` (what every rank cuts out of a dict of full weights under the reference's
+    names): the column-parallel shards tile the output rows, the row-parallel shards tile the input columns, and
+    the row-parallel partial products add up to the full product.  CPU tensors, two ranks."""
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_layers=1, num_heads=4, num_kv_heads=2, head_dim=64,
+                      vocab_size=100)
+    g = torch.Generator().manual_seed(3)
+    full = {"l0.ln1": torch.rand(256, generator=g), "l0.ln2": torch.rand(256, generator=g)}
+    for name, (n, k) in {"q_proj": (256, 256), "k_proj": (128, 256), "v_proj": (128, 256), "o_proj": (256, 256),
+                         "mlp.gate_proj": (512, 256), "mlp.up_proj": (512, 256), "mlp.down_proj": (256, 512)}.items():
+        full[f"l0.{name}.weight"] = torch.randn(n, k, generator=g)
+    shards = []
+    for rank in range(2):
+        m = ResQForwardB200.__new__(ResQForwardB200)
+        m.cfg, m.device, m.ctx = cfg, torch.device("cpu"), tp.TPContext(rank, 2, None)
+        shards.append(m._shard_of(full, 0))
+    f = lambda t: t.float()
+    q = torch.cat([f(s["qkv"][:128]) for s in shards]); k = torch.cat([f(s["qkv"][128:192]) for s in shards])
+    v = torch.cat([f(s["qkv"][192:]) for s in shards])
+    bf = lambda t: t.to(torch.bfloat16).float()
+    assert torch.equal(q, bf(full["l0.q_proj.weight"])) and torch.equal(k, bf(full["l0.k_proj.weight"]))
+    assert torch.equal(v, bf(full["l0.v_proj.weight"]))
+    assert torch.equal(torch.cat([f(s["gate_up"][:256]) for s in shards]), bf(full["l0.mlp.gate_proj.weight"]))
+    assert torch.equal(torch.cat([f(s["gate_up"][256:]) for s in shards]), bf(full["l0.mlp.up_proj.weight"]))
+    assert torch.equal(torch.cat([f(s["o"]) for s in shards], 1), bf(full["l0.o_proj.weight"]))
+    assert torch.equal(torch.cat([f(s["down"]) for s in shards], 1), bf(full["l0.mlp.down_proj.weight"]))
+    x = torch.randn(5, 512, generator=g)
+    part = sum(x[:, tp.row_parallel_cols(512, r, 2)] @ f(shards[r]["down"]).T for r in range(2))
+    assert torch.allclose(part, x @ bf(full["l0.mlp.down_proj.weight"]).T, atol=1e-4)
