@@ -38,7 +38,8 @@ constexpr int kGtN = 16;                                   // MMA N (activation 
 constexpr int kGtXBytes = kGtN * kStageKBytes;             // 2 KiB
 constexpr int kGtSfBytes = 4 * kSfChunk;                   // 2 KiB: four chunks of one 128-row group
 constexpr int kGtStageBytes = kABytes + kGtXBytes + 2 * kGtSfBytes;
-template <int MR> constexpr int kGtStagesFor = MR == 8 ? 8 : 7;   // the partial-sum slots take shared memory too
+constexpr int kGtStagesAll = 4;                            // 4 x 22 KiB in flight per CTA; two CTAs share an SM
+template <int MR> constexpr int kGtStagesFor = kGtStagesAll;
 constexpr uint32_t kGtProducers = 3;                         // warps 0, 2, 3: one thread each, stages round-robin
 constexpr int kGtAccStages = 2;
 constexpr int kGtAccCols = 32;                             // spacing of the two accumulators (16 used)
@@ -47,18 +48,32 @@ constexpr int kGtSfSetCols = 32;                           // 4 MMAs x (4 weight
 constexpr int kGtTmemCols = 128;
 constexpr int kGtThreads = 256;
 constexpr int kGtEpiThreads = 128;
-constexpr int kGtMaxSlices = 8;                            // portable cluster size
+// K slices per tile = CTAs per cluster.  Bounded by the shared memory the partial-sum slots may take if two CTAs
+// (of this launch, or the tail of one launch and the head of the next) are to fit one SM.
+template <int MR> constexpr int kGtMaxSlicesFor = MR == 8 ? 4 : 3;
+constexpr int kGtMaxSlices = 4;
 template <int MR> constexpr int kGtSlotBytesFor = MR * 128 * 4;      // one partial: MR activation rows x 128 weight rows, float32
 template <int MR>
-constexpr size_t kGtSmemBytesFor = 1024 + static_cast<size_t>(kGtStagesFor<MR>) * kGtStageBytes + (kGtMaxSlices - 1) * kGtSlotBytesFor<MR> + 512;
+constexpr size_t kGtSmemBytesFor = 1024 + static_cast<size_t>(kGtStagesFor<MR>) * kGtStageBytes + (kGtMaxSlicesFor<MR> - 1) * kGtSlotBytesFor<MR> + 512;
 static_assert(kGtSfCol0 + 2 * kGtSfSetCols <= kGtTmemCols, "tensor memory budget");
-static_assert(kGtSmemBytesFor<8> <= 232448 && kGtSmemBytesFor<16> <= 232448, "shared memory budget");
+static_assert(2 * (kGtSmemBytesFor<8> + 1024) <= 232448 && 2 * (kGtSmemBytesFor<16> + 1024) <= 232448,
+              "two CTAs per SM (1 KiB per CTA is reserved by the system)");
 
 struct GtMaps {
   CUtensorMap w_lo, x_lo, w_hi, x_hi, sfw_lo, sfx_lo, sfw_hi, sfx_hi;
 };
 
+#ifdef PLQ_GEMV_TRACE
+// Debug builds only: every CTA stamps %globaltimer at its phase boundaries into trace[cta * 16 + phase].
+#define PLQ_GT_STAMP(i) do { g.trace[static_cast<size_t>(blockIdx.x) * 16 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define PLQ_GT_STAMP(i) do { } while (0)
+#endif
+
 struct GtArgs {
+#ifdef PLQ_GEMV_TRACE
+  unsigned long long* trace;
+#endif
   __nv_bfloat16* y;
   int64_t ldy;
   int32_t* status;
@@ -89,14 +104,14 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
 
 // MR = 8 or 16: how many activation rows (accumulator columns) the epilogue handles.
 template <int MR>
-__global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_constant__ GtMaps maps, const GtArgs g) {
+__global__ void __launch_bounds__(kGtThreads, 2) gemv_tc_kernel(const __grid_constant__ GtMaps maps, const GtArgs g) {
   constexpr int kGtStages = kGtStagesFor<MR>;
   constexpr int kGtSlotBytes = kGtSlotBytesFor<MR>;
   constexpr int kGtSlotFloats = MR * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* slots = reinterpret_cast<float*>(smem + static_cast<size_t>(kGtStages) * kGtStageBytes);   // CTA 0: partials of CTAs 1..S-1
-  uint8_t* tail = reinterpret_cast<uint8_t*>(slots) + (kGtMaxSlices - 1) * kGtSlotBytes;
+  uint8_t* tail = reinterpret_cast<uint8_t*>(slots) + (kGtMaxSlicesFor<MR> - 1) * kGtSlotBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
   uint64_t* empty_bar = full_bar + kGtStages;
   uint64_t* acc_full = empty_bar + kGtStages;
@@ -107,6 +122,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
 
   const int warp = warp_index();
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) PLQ_GT_STAMP(0);                     // entry
   const int nslice = static_cast<int>(cluster_nctarank());   // S: CTAs sharing one tile along K
   const int slice = static_cast<int>(cluster_ctarank());
 
@@ -133,12 +149,13 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  if (nslice > 1) {                 // CTA 0's barrier must be initialised before a peer arrives on it
-    cluster_arrive_release();
-    cluster_wait_acquire();
-  }
+  // CTA 0's barrier must be initialised before a peer arrives on it, which a peer does only at the very end of
+  // its work: every CTA arrives on the cluster barrier here and waits on it just before its first remote access
+  // (peers) or before it leaves (CTA 0), by which time the others have long arrived.
+  if (nslice > 1) cluster_arrive_release();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (threadIdx.x == 0) PLQ_GT_STAMP(1);                     // barriers, tensor memory, cluster handshake done
   pdl_launch_dependents();          // the next kernel may be set up and prefetch its weights while this one runs
 
   // This CTA's work: K stages [ks_begin, ks_end) of tiles first_tile, first_tile + tile_step, ...
@@ -183,7 +200,9 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
           for (int ks = ks_begin; ks < ks_end && gs0 < n_init; ++ks, ++gs0)
             if (gs0 % kGtProducers == pid) issue(gs0, first_tile + t * tile_step, ks, true, false);
       }
+      if (pid == 0) PLQ_GT_STAMP(2);                           // early weight loads issued
       pdl_wait();
+      if (pid == 0) PLQ_GT_STAMP(3);                           // previous kernel complete
       if (g.static_b) {
         uint32_t gs0 = 0;
         for (int t = 0; t < my_tiles && gs0 < n_init; ++t)
@@ -221,6 +240,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
         for (int ks = ks_begin; ks < ks_end; ++ks) {
           ok = mbar_wait_bounded(&full_bar[s], phase, abort_flag);
           if (!ok) break;
+          if (t == 0 && ks == ks_begin) PLQ_GT_STAMP(4);       // first stage landed
           tc_fence_after();
           const bool lo = ks < g.lo_stages;
           const int kk = lo ? ks : ks - g.lo_stages;
@@ -266,6 +286,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
         }
         if (!ok) break;
         tc_commit<1>(smem_u32(&acc_full[as]));
+        if (t == my_tiles - 1) PLQ_GT_STAMP(5);                // last MMA issued
         if (++as == kGtAccStages) { as = 0; aphase ^= 1; }
       }
     }
@@ -280,6 +301,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
       bool ok = mbar_wait_bounded_warp(&acc_full[as], aphase, abort_flag);
       ok = epi_all(ok);                               // one decision for the four warps
       if (!ok) break;
+      if (threadIdx.x == 128 && t == my_tiles - 1) PLQ_GT_STAMP(6);   // accumulator complete
       tc_fence_after();
       uint32_t r[MR];
       if constexpr (MR == 8) {
@@ -301,10 +323,12 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
       for (int j = 0; j < MR; ++j) acc[j] = __uint_as_float(r[j]);
       if (slice > 0) {
         // push this slice's partial sums into CTA 0's slot (slice - 1), then arrive (release) on its barrier
+        cluster_wait_acquire();                         // set-up of every CTA of the cluster is complete
         const uint32_t dst = map_to_cta(smem_u32(slots), 0u) + static_cast<uint32_t>((slice - 1) * kGtSlotBytes + trow * 4);
 #pragma unroll
         for (int j = 0; j < MR; ++j) st_cluster_f32(dst + j * 512, acc[j]);
         mbar_arrive_cluster(map_to_cta(smem_u32(red_bar), 0u));
+        if (threadIdx.x == 128) PLQ_GT_STAMP(7);            // partial pushed to CTA 0
         continue;
       }
       if (nslice > 1) {
@@ -314,6 +338,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
         if (!epi_all(got != 0)) break;
         while (!mbar_try_wait_cluster(red_bar, 0u)) {   // completed: gives every thread the acquire
         }
+        if (threadIdx.x == 128) PLQ_GT_STAMP(7);            // all partials have arrived
         for (int sl = 0; sl < nslice - 1; ++sl) {
 #pragma unroll
           for (int j = 0; j < MR; ++j) acc[j] += slots[sl * kGtSlotFloats + j * 128 + trow];
@@ -325,6 +350,7 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
         for (int j = 0; j < MR; ++j)
           if (j < g.m) g.y[static_cast<size_t>(j) * g.ldy + row] = __float2bfloat16_rn(acc[j]);
       }
+      if (threadIdx.x == 128 && t == my_tiles - 1) PLQ_GT_STAMP(8);   // output stored
     }
   }
 
@@ -336,15 +362,21 @@ __global__ void __launch_bounds__(kGtThreads, 1) gemv_tc_kernel(const __grid_con
     while (clock64() - t0 < 400000ll) __nanosleep(1000);
     __syncthreads();
   }
-  if (nslice > 1) {                 // CTA 0's shared memory is written by its peers: leave together
-    cluster_arrive_release();
-    cluster_wait_acquire();
-  }
+  // Only CTA 0's shared memory is written remotely, and CTA 0 has waited for every partial before it gets here:
+  // nobody needs to wait for anybody to leave.  Threads that have not consumed the set-up phase of the cluster
+  // barrier yet (everything but the epilogue warps of CTAs 1..) do it now; it completed long ago.
+  if (nslice > 1 && !(slice > 0 && warp >= 4 && my_tiles > 0)) cluster_wait_acquire();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kGtTmemCols);
   }
+  if (threadIdx.x == 0) PLQ_GT_STAMP(9);                     // leaving
 }
+
+#ifdef PLQ_GEMV_TRACE
+static unsigned long long* g_gt_trace = nullptr;   // set by plq_debug_set_gemv_trace; launch i writes at i * 148 * 16
+static int g_gt_launch = 0;
+#endif
 
 // ---- host side --------------------------------------------------------------------------------
 // How many clusters of each size the device can hold at once (one CTA per SM, clusters inside a GPC);
@@ -359,7 +391,7 @@ static int gt_max_clusters(int slices) {
     if (cudaFuncSetAttribute(gemv_tc_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kGtSmemBytesFor<MR>)) != cudaSuccess)
       return 0;
-    for (int s = 1; s <= kGtMaxSlices; ++s) {
+    for (int s = 1; s <= kGtMaxSlicesFor<MR>; ++s) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(static_cast<unsigned>(s * 64), 1, 1);
       cfg.blockDim = dim3(kGtThreads, 1, 1);
@@ -388,12 +420,12 @@ static void gt_plan(int64_t n, int64_t k_lo, int64_t k_hi, int sms, int* slices,
   const int tiles = static_cast<int>((n + kBM - 1) / kBM);
   const int k_stages = static_cast<int>((k_lo / 64 + 3) / 4 + (k_hi + 127) / 128);
   int s = sms / tiles;
-  if (s > kGtMaxSlices) s = kGtMaxSlices;
+  if (s > kGtMaxSlicesFor<MR>) s = kGtMaxSlicesFor<MR>;
   if (s > k_stages) s = k_stages;
   while (s > 1 && gt_max_clusters<MR>(s) < tiles) --s;
   if (s < 1) s = 1;
   *slices = s;
-  *grid = s > 1 ? tiles * s : (tiles < sms ? tiles : sms);
+  *grid = s > 1 ? tiles * s : (tiles < 2 * sms ? tiles : 2 * sms);      // two CTAs fit an SM
 }
 
 template <int MR>
@@ -451,6 +483,10 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
   g.hi_stages = static_cast<int>((k_hi + 127) / 128);
   g.tiles = static_cast<int>((n + kBM - 1) / kBM);
   g.static_b = (flags & PLQ_GEMV_STATIC_B) ? 1 : 0;
+#ifdef PLQ_GEMV_TRACE
+  if (!g_gt_trace) return PLQ_ERR_NULL;
+  g.trace = g_gt_trace + static_cast<size_t>(g_gt_launch++ % 64) * 256 * 16;
+#endif
 
   GtMaps tm;
   memset(&tm, 0, sizeof(tm));
@@ -470,3 +506,10 @@ extern "C" int plq_gemv_tc(const void* a_lo_codes, const void* a_lo_sf, const vo
   return m <= 8 ? gt_launch<8>(tm, g, n, k_lo, k_hi, static_cast<cudaStream_t>(stream))
                 : gt_launch<16>(tm, g, n, k_lo, k_hi, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef PLQ_GEMV_TRACE
+extern "C" __attribute__((visibility("default"))) void plq_debug_set_gemv_trace(void* buf) {
+  plq::g_gt_trace = static_cast<unsigned long long*>(buf);
+  plq::g_gt_launch = 0;
+}
+#endif

@@ -367,7 +367,8 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
           const uint32_t uu[4] = {w2[c].x, w2[c].y, w2[c].z, w2[c].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint32_t t = f32x2_to_bf16x2(silu_det(bf16lo_to_f32(ww[i])), silu_det(bf16hi_to_f32(ww[i])));   // SiLU, to bf16
+            const float2 sl = silu_det2(make_float2(bf16lo_to_f32(ww[i]), bf16hi_to_f32(ww[i])));
+            const uint32_t t = f32x2_to_bf16x2(sl.x, sl.y);                                                        // SiLU, to bf16
             const float2 prod = __fmul2_rn(make_float2(bf16lo_to_f32(t), bf16hi_to_f32(t)),
                                            make_float2(bf16lo_to_f32(uu[i]), bf16hi_to_f32(uu[i])));
             v[4 * c + i] = round_bf16_pair(prod);                                                                  // product, to bf16

@@ -145,9 +145,37 @@ __device__ __forceinline__ float exp_det(float x) {
   return __fmul_rn(__fmul_rn(p, s1), s2);
 }
 
+// The same list of operations on two values at once (packed float32x2 multiplies and adds round each element like
+// their scalar forms, so the results are those of exp_det).
+__device__ __forceinline__ float2 exp_det2(float2 x) {
+  x.x = fminf(fmaxf(x.x, -100.0f), 100.0f);
+  x.y = fminf(fmaxf(x.y, -100.0f), 100.0f);
+  const float2 magic = make_float2(12582912.0f, 12582912.0f), nmagic = make_float2(-12582912.0f, -12582912.0f);
+  const float2 n = __fadd2_rn(__fadd2_rn(__fmul2_rn(x, make_float2(1.44269502162933349609375f, 1.44269502162933349609375f)), magic), nmagic);
+  // x - n * c == x + n * (-c): the product only changes sign
+  float2 r = __fadd2_rn(x, __fmul2_rn(n, make_float2(-0.693359375f, -0.693359375f)));
+  r = __fadd2_rn(r, __fmul2_rn(n, make_float2(2.12194440e-4f, 2.12194440e-4f)));
+  float2 p = make_float2(1.98412701138295233249664306640625e-4f, 1.98412701138295233249664306640625e-4f);
+  const float c[7] = {1.388888922519981861114501953125e-3f, 8.3333337679505348205566406250e-3f,
+                      4.16666679084300994873046875e-2f, 0.1666666716337203979492187500f, 0.5f, 1.0f, 1.0f};
+#pragma unroll
+  for (int i = 0; i < 7; ++i) p = __fadd2_rn(__fmul2_rn(p, r), make_float2(c[i], c[i]));
+  const int n0 = __float2int_rn(n.x), n1 = __float2int_rn(n.y);
+  const int h0 = n0 >> 1, h1 = n1 >> 1;
+  const float2 s1 = make_float2(__uint_as_float(static_cast<uint32_t>(h0 + 127) << 23),
+                                __uint_as_float(static_cast<uint32_t>(h1 + 127) << 23));
+  const float2 s2 = make_float2(__uint_as_float(static_cast<uint32_t>(n0 - h0 + 127) << 23),
+                                __uint_as_float(static_cast<uint32_t>(n1 - h1 + 127) << 23));
+  return __fmul2_rn(__fmul2_rn(p, s1), s2);
+}
+
 // SiLU(g) = g / (1 + exp(-g)), float32, IEEE division (torch.nn.functional.silu on a bf16 tensor computes in
 // float32 and rounds once; the caller does that rounding).
 __device__ __forceinline__ float silu_det(float g) { return __fdiv_rn(g, __fadd_rn(1.0f, exp_det(-g))); }
+__device__ __forceinline__ float2 silu_det2(float2 g) {
+  const float2 d = __fadd2_rn(make_float2(1.0f, 1.0f), exp_det2(make_float2(-g.x, -g.y)));
+  return make_float2(__fdiv_rn(g.x, d.x), __fdiv_rn(g.y, d.y));
+}
 
 #endif  // __CUDACC__
 }  // namespace plq
