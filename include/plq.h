@@ -153,6 +153,24 @@ PLQ_API int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* 
                                            void* stream);
 
 /*
+ * One column block of GPTQ for the block-scaled formats: columns [col0, col0 + count), count <= 128, of the
+ * float32 weight w[rows, k] (which already carries the corrections of the earlier blocks) are rounded one after
+ * the other - each against the block scale frozen beforehand (`lo_sf` [rows, (k - k_hi)/16] E4M3 bytes for the
+ * NVFP4 columns, `hi_sf` [rows, k_hi/32] E8M0 bytes for the last k_hi, both row-major) - and the rounding error of
+ * column i, divided by hinv[i, i], is folded into the later columns of the block with row i of `hinv` (the upper
+ * Cholesky factor of the inverse Hessian, [k, k]).  Outputs: q[rows, k] receives the dequantised values of the
+ * block's columns, err[rows, count] the scaled errors (the caller applies them to the columns behind the block:
+ * w[:, col0 + count:] -= err @ hinv[col0 : col0 + count, col0 + count:]), codes[rows, k] one code per element.
+ * `w` itself is not modified.
+ * Replaces the per-column inner loop of GPTQ.fasterquant with quantize_column_with_frozen_scale,
+ * promix/quantize/gptq.py:142-205 and promix/quantize/quant_utils.py:616-657.
+ */
+PLQ_API int plq_gptq_block_frozen(const void* w_f32, int64_t ldw, const void* hinv_f32, int64_t ldh,
+                                  const void* lo_sf, const void* hi_sf, int64_t rows, int64_t k, int64_t k_hi,
+                                  int64_t col0, int64_t count, void* q_f32, int64_t ldq, void* err_f32,
+                                  void* codes_u8, void* stream);
+
+/*
  * Dequantise a packed matrix back to bf16 [rows, k_lo + k_hi] (= the fake quantiser's return
  * value, promix/quantize/quant_utils.py:750-751, :706-707).
  */

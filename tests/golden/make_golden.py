@@ -180,6 +180,32 @@ def main(ref_root):
                         w_checksum=np.uint64(int(bf16_bits(W).astype(np.uint64).sum())),
                         xr=bf16_bits(Xr), wr_rows=bf16_bits(Wr[:4]), wq_rows=bf16_bits(Wq[:4]),
                         y_bf16=bf16_bits(Y_bf16), y_f32=Y_f32.numpy())
+    # ---------------- gptq_frozen ---------------------------------------------------------
+    # The reference's own GPTQ class on a seeded single-block problem (K = blocksize = 128, so the comparison
+    # involves no cross-block matmul, whose float32 summation order is unspecified): 96 output rows, NVFP4 for the
+    # first 64 input columns and MXFP8 for the last 64, Hessian from 512 synthetic calibration rows.  The factor
+    # of the inverse Hessian that the loop consumes is recomputed here exactly as gptq.py:125-141 does and stored,
+    # since LAPACK results are not portable bit for bit.
+    from promix.quantize.gptq import GPTQ
+    from promix.quantize.kv_quant import WeightQuantizer
+    g = torch.Generator().manual_seed(11)
+    n_out, k, k_hi = 96, 128, 64
+    Wg = (torch.randn(n_out, k, generator=g) * 0.02).to(torch.bfloat16)
+    Xc = torch.randn(512, k, generator=g) * (1.0 + 3.0 * torch.rand(k, generator=g))
+    layer = torch.nn.Linear(k, n_out, bias=False)
+    layer.weight.data = Wg.float().clone()
+    gq = GPTQ(layer, mixed_precision=True, high_bits_length=k_hi, low_bits_length=0)
+    gq.quantizer = WeightQuantizer(); gq.quantizer.configure("nvfp4", perchannel=True, sym=True, mse=False)
+    gq.high_quantizer = WeightQuantizer(); gq.high_quantizer.configure("mxfp8", perchannel=True, sym=True, mse=False)
+    gq.add_batch(Xc, None)
+    Hm = gq.H.clone()
+    Hd = Hm.clone()
+    Hd[torch.arange(k), torch.arange(k)] += 0.01 * torch.mean(torch.diag(Hd))
+    Hinv = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hd)), upper=True)
+    gq.fasterquant(blocksize=128, percdamp=0.01, groupsize=-1, actorder=False)
+    Qg = layer.weight.data.float()
+    np.savez_compressed(os.path.join(HERE, "gptq_frozen.npz"), w=bf16_bits(Wg), hinv=Hinv.numpy(), q=Qg.numpy(),
+                        k_hi=np.int64(k_hi))
     print("golden fixtures written to", HERE)
 
 

@@ -122,3 +122,38 @@ def test_linear_config0_against_reference(golden_dir):
     yb = F.bf16_bits_to_f32(F.f32_to_bf16_bits(y)); refb = F.bf16_bits_to_f32(g["y_bf16"])
     rel_b = np.linalg.norm(yb - refb) / np.linalg.norm(refb)
     assert rel_b < 3e-3, rel_b
+
+
+def test_gptq_frozen_scale_loop_against_reference(golden_dir):
+    """oracle/gptq.py against the output of the reference's own GPTQ class (FP path, scales frozen on the original
+    weight) on a seeded single-block problem: every rounded weight identical."""
+    from oracle import gptq as G
+    g = _load(golden_dir, "gptq_frozen.npz")
+    w = F.bf16_bits_to_f32(g["w"])
+    k_hi = int(g["k_hi"])
+    frozen = F.pack_mixed(w, k_hi)                       # the scales round-to-nearest packing gives the original weight
+    q, err, codes = G.gptq_block_frozen(w, g["hinv"], frozen["lo_sf"], frozen["hi_sf"], k_hi, 0, w.shape[1])
+    assert np.array_equal(q, g["q"])
+    # the rounding differs from plain round-to-nearest on a fair share of the elements (otherwise the test says little)
+    rtn = F.dequant_mixed(frozen)
+    assert 0.02 < np.mean(q != rtn) < 0.6
+    # codes and values are consistent
+    k_lo = w.shape[1] - k_hi
+    assert np.array_equal(F.dequant_nvfp4(codes[:, :k_lo], frozen["lo_sf"]), q[:, :k_lo])
+    assert np.array_equal(F.dequant_mxfp8(codes[:, k_lo:], frozen["hi_sf"]), q[:, k_lo:])
+
+
+def test_reference_quantiser_staged_for_the_benchmark_agrees_with_the_oracle():
+    """When oracle/_ref holds the staged copy of the reference's quantiser (oracle/build_ref.py), its ActQuantizer
+    must return exactly what the oracle dequantises - the same statement as the fixtures, on fresh data."""
+    torch = pytest.importorskip("torch")
+    from oracle import build_ref
+    if not build_ref.available():
+        pytest.skip("oracle/_ref is not staged on this machine")
+    qu, _ = build_ref.load()
+    x = torch.randn(32, 512, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    q = qu.ActQuantizer()
+    q.configure(bits="nvfp4", high_bits="mxfp8", high_bits_length=64)
+    got = q(x).float().numpy()
+    xf = F.bf16_bits_to_f32(x.view(torch.int16).numpy().view(np.uint16))
+    assert np.array_equal(got, F.round_to_bf16(F.dequant_mixed(F.pack_mixed(xf, 64))))
