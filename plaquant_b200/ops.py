@@ -58,6 +58,8 @@ def status_word(device) -> torch.Tensor:
     dev = torch.device(device)
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _status_words:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the status word must exist before a CUDA-graph capture: run the op once eagerly first")
         _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
     return _status_words[key]
 
@@ -233,6 +235,9 @@ def gemv_workspace(device, n: int) -> torch.Tensor:
     need = _lib.lib().plq_gemv_workspace_bytes(n)
     ws = _gemv_ws.get(key)
     if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the GEMV workspace must exist before a CUDA-graph capture: call gemv() (or "
+                               "gemv_workspace()) once on this stream before capturing")
         ws = torch.zeros(need, dtype=torch.uint8, device=f"cuda:{key[0]}")
         _gemv_ws[key] = ws
     return ws

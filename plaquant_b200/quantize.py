@@ -95,6 +95,9 @@ class QuantizedLinear:
         self._gemm_w = ops.PackedMatrix(n, k_lo, k_hi, lo_c, _tile_sf(lo_s), hi_c,
                                         _tile_sf(hi_s) if k_hi else torch.zeros(0, dtype=torch.uint8, device=dev),
                                         ops.SF_TILED)
+        # forward() declares the weights static (PLQ_GEMV_STATIC_B): the decode GEMV may then fetch them before the
+        # kernels launched ahead of it have finished, so everything that produced them must be complete by now
+        torch.cuda.current_stream(dev).synchronize()
 
     def to(self, device):
         self.w_main_int = self.w_main_int.to(device)
