@@ -419,7 +419,7 @@ template <int MR>
 static void gt_plan(int64_t n, int64_t k_lo, int64_t k_hi, int sms, int* slices, int* grid) {
   const int tiles = static_cast<int>((n + kBM - 1) / kBM);
   const int k_stages = static_cast<int>((k_lo / 64 + 3) / 4 + (k_hi + 127) / 128);
-  int s = sms / tiles;
+  int s = (2 * sms) / tiles;                           // two CTAs fit an SM
   if (s > kGtMaxSlicesFor<MR>) s = kGtMaxSlicesFor<MR>;
   if (s > k_stages) s = k_stages;
   while (s > 1 && gt_max_clusters<MR>(s) < tiles) --s;

@@ -170,6 +170,53 @@ __device__ __forceinline__ void stage_segment(uint32_t seg_smem, const uint4* sr
   }
 }
 
+// Tensor-parallel prologue: one segment of x = bf16(sum over the ranks of their partial outputs), float32 in rank
+// order so that every rank computes the same bits.  Each rank's 4 KB of the segment is read with consecutive
+// addresses across the warp (whole 128-byte lines over NVLink), B pieces of all ranks in flight at a time, and the
+// sum goes to shared memory in the layout stage_segment produces.  `off0` = index of the lane's first 16-byte piece.
+template <int B, int W>
+__device__ __forceinline__ void reduce_segment(uint8_t* seg, const uint4* const* peer_x, int world, size_t off0,
+                                               int npieces, int lane) {
+  const uint32_t q = static_cast<uint32_t>(lane) >> 3;
+  const uint32_t x = ((static_cast<uint32_t>(lane) & 7u) ^ q) << 4;
+  uint8_t* d_even = seg + q * 128 + x;
+  uint8_t* d_odd = seg + q * 128 + (x ^ 64u);
+#pragma unroll
+  for (int jb = 0; jb < 8; jb += B) {
+    uint4 t[B][W];
+#pragma unroll
+    for (int jj = 0; jj < B; ++jj) {
+      const bool valid = 32 * (jb + jj) + lane < npieces;
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        t[jj][r] = make_uint4(0, 0, 0, 0);
+        if (r < world && valid)
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(t[jj][r].x), "=r"(t[jj][r].y), "=r"(t[jj][r].z), "=r"(t[jj][r].w)
+                       : "l"(peer_x[r] + off0 + 32 * (jb + jj))
+                       : "memory");
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < B; ++jj) {
+      float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        if (r < world) {
+          const uint32_t tt[4] = {t[jj][r].x, t[jj][r].y, t[jj][r].z, t[jj][r].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            acc[i] = __fadd2_rn(acc[i], make_float2(bf16lo_to_f32(tt[i]), bf16hi_to_f32(tt[i])));
+        }
+      }
+      const int j = jb + jj;
+      *reinterpret_cast<uint4*>(((j & 1) ? d_odd : d_even) + 512 * j) =
+          make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
+                     f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
+    }
+  }
+}
+
 // The lane's own eight pieces, register run 0 first; `xr` = ((lane & 7) ^ (4 if the runs are swapped)) << 4.
 __device__ __forceinline__ void read_line(const uint8_t* seg, int lane, uint32_t xr, uint4 (&w)[8]) {
   const uint8_t* line = seg + lane * 128;
@@ -222,7 +269,8 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     t.seg = u - t.row * wpr;
     return t;
   };
-  constexpr bool kStageX = PRO != 3;                // prologue 3 reads x from the peers, straight into registers
+  constexpr bool kStageX = true;                    // x always passes through shared memory ...
+  constexpr bool kCopyX = PRO != 3;                 // ... copied there, or (prologue 3) summed there from the peers
   constexpr bool kStageX2 = PRO != 0;
   constexpr int kOperands = (kStageX ? 1 : 0) + (kStageX2 ? 1 : 0);
   const int stage_bytes = kOperands * nwarps * kSegBytes;           // one group of rows, all staged operands
@@ -235,7 +283,7 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     const Unit t = unit_of(group);
     const int n = t.row < a.rows ? min(max(k8 - 256 * t.seg, 0), 256) : 0;     // 16-byte pieces of the segment inside the row
     const size_t r0 = static_cast<size_t>(t.row < a.rows ? t.row : 0);
-    if constexpr (kStageX) stage_segment(smem_u32(xs0 + slot * stage_bytes), a.x + r0 * a.ldx8 + 256 * t.seg, n, lane);
+    if constexpr (kCopyX) stage_segment(smem_u32(xs0 + slot * stage_bytes), a.x + r0 * a.ldx8 + 256 * t.seg, n, lane);
     if constexpr (kStageX2) stage_segment(smem_u32(x2s0 + slot * stage_bytes), a.x2 + r0 * ld2 + 256 * t.seg, n, lane);
   };
 
@@ -312,51 +360,20 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
       cp_async_wait_pending(a.stages - 1);          // the oldest group in flight is this one
       if (NORM && iter == 0) __syncthreads();       // gamma was staged by the warps of the CTA's first row
       else __syncwarp();
+      if constexpr (PRO == 3) {
+        // this warp's segment of x, summed over the ranks into the x slot (warp-local, like the copies)
+        const int n = row_ok ? min(max(k8 - 256 * unit.seg, 0), 256) : 0;
+        const size_t off0 = static_cast<size_t>(row_ok ? row : 0) * k8 + 256 * unit.seg + lane;
+        if (a.world <= 4) reduce_segment<4, 4>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
+        else reduce_segment<2, 8>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
+        __syncwarp();
+      }
       if constexpr (kStageX) read_line(xs0 + slot * stage_bytes, lane, xr, w);
       if constexpr (kStageX2) read_line(x2s0 + slot * stage_bytes, lane, xr, w2);
       __syncwarp();                                 // every lane has its pieces: the slot is free again
       if (group + a.stages * stride < ngroups) stage_group(group + a.stages * stride, slot);
       cp_async_commit();
       if (++slot == a.stages) slot = 0;
-      if constexpr (PRO == 3) {
-        // x = bf16(sum over the ranks), float32 in rank order (every rank computes the same bits).  The peer loads
-        // of two of the lane's eight pieces are all issued before any of them is used.
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          uint4 t[2][8];
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int piece = 2 * h + jj;
-            const int e = (piece < 4 ? in0 : in1) + 8 * (piece & 3);
-            const bool ok = piece < 4 ? ok0 : ok1;
-            const size_t off = static_cast<size_t>(row) * k8 + (e >> 3);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              t[jj][r] = make_uint4(0, 0, 0, 0);
-              if (r < a.world && ok)
-                asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(t[jj][r].x), "=r"(t[jj][r].y), "=r"(t[jj][r].z), "=r"(t[jj][r].w)
-                             : "l"(a.peer_x[r] + off)
-                             : "memory");
-            }
-          }
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (r < a.world) {
-                const uint32_t tt[4] = {t[jj][r].x, t[jj][r].y, t[jj][r].z, t[jj][r].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  acc[i] = __fadd2_rn(acc[i], make_float2(bf16lo_to_f32(tt[i]), bf16hi_to_f32(tt[i])));
-              }
-            }
-            w[2 * h + jj] = make_uint4(f32x2_to_bf16x2(acc[0].x, acc[0].y), f32x2_to_bf16x2(acc[1].x, acc[1].y),
-                                       f32x2_to_bf16x2(acc[2].x, acc[2].y), f32x2_to_bf16x2(acc[3].x, acc[3].y));
-          }
-        }
-      }
       if constexpr (PRO == 0) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) unpack8(w[c], v + 4 * c);
@@ -686,7 +703,7 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.ngroups = static_cast<int>(groups);
   // shared memory: `stages` groups of rows in flight (each: the staged operands of all warps) + gamma.  Kernels
   // that do little arithmetic per byte (no norm) need more bytes in flight to cover the HBM latency.
-  const int stage_bytes = ((pro != 3) + (pro != 0)) * (threads / 32) * kSegBytes;
+  const int stage_bytes = (1 + (pro != 0)) * (threads / 32) * kSegBytes;
   const int gamma_bytes = norm ? (lanes / 32) * 2 * kSegBytes : 0;      // float32 copy of the norm weights
   int stages = (pro == 0 && !norm) ? 3 : 2;
   while (stages > 1 && 4 * (stages * stage_bytes + gamma_bytes) > 216 * 1024) --stages;   // keep four CTAs per SM
