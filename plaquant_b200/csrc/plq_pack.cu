@@ -705,8 +705,15 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   // that do little arithmetic per byte (no norm) need more bytes in flight to cover the HBM latency.
   const int stage_bytes = (1 + (pro != 0)) * (threads / 32) * kSegBytes;
   const int gamma_bytes = norm ? (lanes / 32) * 2 * kSegBytes : 0;      // float32 copy of the norm weights
+#ifndef PLQ_PACK_MAX_STAGES
+#define PLQ_PACK_MAX_STAGES 3
+#endif
+#ifndef PLQ_PACK_CTAS_PER_SM
+#define PLQ_PACK_CTAS_PER_SM 4
+#endif
   int stages = (pro == 0 && !norm) ? 3 : 2;
-  while (stages > 1 && 4 * (stages * stage_bytes + gamma_bytes) > 216 * 1024) --stages;   // keep four CTAs per SM
+  if (stages > PLQ_PACK_MAX_STAGES) stages = PLQ_PACK_MAX_STAGES;
+  while (stages > 1 && PLQ_PACK_CTAS_PER_SM * (stages * stage_bytes + gamma_bytes + 1024) > 224 * 1024) --stages;   // keep that many CTAs per SM
   a.stages = stages;
   const int smem = stages * stage_bytes + gamma_bytes;
   auto launch = [&](void (*kernel)(const PackArgs)) -> int {
