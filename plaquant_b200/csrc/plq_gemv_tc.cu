@@ -4,11 +4,13 @@
 // and the activations the N-side one (m rows, zero-filled to 16 by the TMA box), so the packed
 // NVFP4 / MXFP8 weight bytes go HBM -> shared memory (TMA) -> tensor core and no thread ever
 // touches, converts or scales them.  The kernel is bound by how fast the weight bytes stream in:
-// a ring of 22 KiB stages (16 KiB of weight codes, 2 KiB of weight scales, 2 + 2 KiB of
-// activation codes and scales, which come from L2) keeps ~140 KiB per SM in flight.
+// a ring of four 22 KiB stages (16 KiB of weight codes, 2 KiB of weight scales, 2 + 2 KiB of
+// activation codes and scales, which come from L2).  A CTA takes 104 KiB of shared memory so that two
+// CTAs share an SM: ~176 KiB per SM in flight, and the CTAs of the next launch can set up and prefetch
+// their weights while the previous launch's are still finishing.
 //
-// Work split.  A 128-row tile of W is the unit of output.  When there are fewer tiles than half
-// the SMs, each tile is given to a thread-block cluster of S CTAs (S <= 8, all clusters resident
+// Work split.  A 128-row tile of W is the unit of output.  When there are fewer tiles than CTA slots,
+// each tile is given to a thread-block cluster of S CTAs (S <= 4, all clusters resident
 // at once), CTA r taking the r-th slice of the K stages; CTAs 1..S-1 push their float32 partial
 // sums [8 or 16 activation rows, 128]
 // into CTA 0's shared memory (distributed shared memory, one hop) and arrive on its barrier, and
@@ -16,8 +18,8 @@
 // No scratch memory in HBM is needed.  Otherwise S = 1 and CTAs loop over whole tiles.
 //
 // Programmatic dependent launch: the kernel is launched so that it may start while the previous
-// kernel in the stream drains.  Barrier set-up, tensor-memory allocation, descriptor prefetch and
-// the cluster handshake happen before griddepcontrol.wait; every load and store after it - except
+// kernel in the stream drains.  Barrier set-up, tensor-memory allocation and descriptor prefetch
+// happen before griddepcontrol.wait; every load and store after it - except
 // that a caller who declares the weights static (flag PLQ_GEMV_STATIC_B) lets the first ring fill
 // of weight bytes be requested before the wait.
 //
