@@ -129,19 +129,24 @@ def host_threads() -> int:
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
-def _sample_tensors(torch):
+SHAPES_70B = [("qkv", 8192, 10240, True), ("o", 8192, 8192, False), ("gate_up", 8192, 57344, True),
+              ("down", 28672, 8192, False)]     # one Llama-3-70B decoder layer's linears (fused q/k/v and gate/up)
+
+
+def _sample_tensors(torch, shapes=None, m=None, n_rows=None):
+    shapes, m, n_rows = shapes or SHAPES, m or SAMPLE_M, n_rows or SAMPLE_N
     g = torch.Generator().manual_seed(1234)
     out = []
-    for name, k, n, norm in SHAPES:
-        x = torch.randn(SAMPLE_M, k, generator=g)
+    for name, k, n, norm in shapes:
+        x = torch.randn(m, k, generator=g)
         x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
-        w = torch.randn(SAMPLE_N, k, generator=g) * 0.02
+        w = torch.randn(n_rows, k, generator=g) * 0.02
         gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
         out.append((name, k, x.to(torch.bfloat16), w.to(torch.bfloat16), gamma if norm else None))
     return out
 
 
-def _cpu_step_reference(torch):
+def _cpu_step_reference(torch, shapes=None, m=None, n_rows=None):
     """One step = for each of the four shapes: [RMSNorm] -> block-Hadamard(128) as a float32 matmul with the
     reference's own matrix -> the reference's ActQuantizer (bits "nvfp4", high_bits "mxfp8", last K/32 channels)
     -> torch's bf16 F.linear against weights the reference's quantiser prepared once (untimed)."""
@@ -157,7 +162,7 @@ def _cpu_step_reference(torch):
 
     work = []
     with torch.no_grad():
-        for name, k, x, w, gamma in _sample_tensors(torch):
+        for name, k, x, w, gamma in _sample_tensors(torch, shapes, m, n_rows):
             k_hi = k // 32
             wr = rotate(w)
             wq = torch.cat([qu.fake_quantize_nvfp4(wr[:, : k - k_hi]), qu.fake_quantize_mxfp8(wr[:, k - k_hi:])], -1)
@@ -175,7 +180,7 @@ def _cpu_step_reference(torch):
     return step, "reference", torch.get_num_threads()
 
 
-def _cpu_step_port(torch):
+def _cpu_step_port(torch, shapes=None, m=None, n_rows=None):
     """The same step on the C port (oracle/plq_oracle.c, OpenMP) with torch's float32 matmul for the product."""
     import numpy as np
     from oracle import cport
@@ -186,7 +191,7 @@ def _cpu_step_port(torch):
         return t.contiguous().view(torch.int16).numpy().view(np.uint16)
 
     work = []
-    for name, k, x, w, gamma in _sample_tensors(torch):
+    for name, k, x, w, gamma in _sample_tensors(torch, shapes, m, n_rows):
         wdq = torch.from_numpy(cport.dequant(cport.prepare(bits(w), k // 32, hadamard=True)))
         work.append((bits(x), None if gamma is None else bits(gamma), k, wdq))
 
@@ -224,6 +229,27 @@ def config_dict(n_gpus):
                         "14336->4096), K split 31/32 NVFP4 + 1/32 MXFP8, RMSNorm/Hadamard/pack on device",
             "m_tokens": M_TOKENS, "l2": "per-step working set ~1.1 GB >> 126 MB L2, no flush needed",
             "parallelism": f"replicas x{n_gpus}" if n_gpus > 1 else "single GPU"}
+
+
+def cpu_model_estimate(budget_s: float = 8.0):
+    """configs[4] on the host, extrapolated: the CPU arm's code on 64 token rows x 1024 weight rows of each of the
+    four linears of one Llama-3-70B decoder layer (full K), and from its rate the tokens/s the 80 layers' linears
+    alone would allow (a full 70B forward does not fit a host's memory or a benchmark's time)."""
+    import torch
+    from oracle import build_ref
+    m, n_rows = 64, 1024
+    step, kind, cores = (_cpu_step_reference if build_ref.available() else _cpu_step_port)(torch, SHAPES_70B, m, n_rows)
+    step()
+    done, t0 = 0, time.perf_counter()
+    while done == 0 or time.perf_counter() - t0 < budget_s:
+        step()
+        done += 1
+    dt = (time.perf_counter() - t0) / done
+    rate = sum(2.0 * m * n_rows * k for _, k, _, _ in SHAPES_70B) / dt               # flop/s on the sample
+    per_token = 80 * sum(2.0 * n * k for _, k, n, _ in SHAPES_70B)                    # flop per token, linears only
+    return {"tokens_per_s": rate / per_token, "tflops": rate / 1e12, "cores": cores, "kind": kind, "extrapolated": True,
+            "sample": f"{m} token rows x {n_rows} weight rows of each of one layer's four linears, full K, x 80 layers; "
+                      "attention, LM head and weight quantisation not counted"}
 
 
 def main_reference(args, rank):
@@ -437,6 +463,8 @@ def main_ours(args, rank, local_rank, world):
         try:
             line["cpu_baseline"] = {k: v for k, v in run_cpu_sample(20, 1, budget_s=15.0).items()
                                     if k not in ("ms_per_step", "steps_timed")}
+            if model_tp is not None:
+                model_tp["cpu_baseline_extrapolated"] = cpu_model_estimate()
         except Exception as exc:  # the checker could not be built or staged on this host
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
     print(json.dumps(line), flush=True)
