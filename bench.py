@@ -483,8 +483,10 @@ def run_model_tp(args, torch, plq, rank, world, dev, peaks):
     ctx = tp.TPContext(rank, world, None)
     cfg = LlamaConfig.llama3_70b()
     layers = args.tp_layers
-    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0)
     batch, prefill, decode = args.batch, args.prefill, args.decode
+    scattered = args.fused_reduce and args.scatter_prefill and world > 1 and (batch * prefill) % world == 0
+    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0,
+                            scatter_prefill_rows=batch * prefill if scattered else 0)
     ids = torch.randint(0, cfg.vocab_size, (batch, prefill), generator=torch.Generator().manual_seed(40)).to(dev)
 
     def sync():
@@ -545,7 +547,9 @@ def run_model_tp(args, torch, plq, rank, world, dev, peaks):
             "scaling": "strong", "parallelism": f"tp{world}", "layers": layers, "of_layers": cfg.num_layers,
             "batch": batch, "prefill_tokens": prefill, "decode_steps": decode, "ms": ms, "prefill_ms": prefill_ms,
             "decode_ms": decode_ms, "decode_ms_per_step": step_ms, "ranks_agree_on_tokens": same,
-            "reduce": "fused into the RMSNorm-quant kernel over peer memory (decode), NCCL (prefill)" if (args.fused_reduce and world > 1)
+            "reduce": ("fused into the RMSNorm-quant kernel over peer memory: all-reduce form (decode), "
+                       + ("reduce-scatter + all-gather of the packed rows (prefill)" if scattered else "NCCL (prefill)"))
+                      if (args.fused_reduce and world > 1)
                       else ("NCCL" if world > 1 else "none (one rank)"),
             "allreduce": ar,
             "decode_roofline": {"bound": "hbm", "bytes_per_step_per_rank": step_bytes,
@@ -803,6 +807,9 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--variant", default=None, choices=["128x128", "128x256", "pair256x256"])
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--nccl-prefill", dest="scatter_prefill", action="store_false",
+                    help="model_tp: all-reduce the prefill's row-parallel outputs with NCCL instead of the fused "
+                         "reduce-scatter / all-gather kernel")
     ap.add_argument("--nccl-reduce", dest="fused_reduce", action="store_false",
                     help="model workload: NCCL all-reduces in the decode step instead of the reduction fused into "
                          "the RMSNorm-quant kernel over peer memory")

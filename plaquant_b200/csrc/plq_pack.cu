@@ -48,6 +48,11 @@ struct PackArgs {
   int32_t* status;               // receives PLQ_DEV_TIMEOUT if a rank does not show up
   int world, rank;
   int buffer_index;              // which of the two buffer sets peer_x names (0 / 1), or -1: checked against the call count
+  // prologue 3, scattered form: this rank handles rows [row0, row0 + rows) of the ranks' [total, k] buffers and
+  // stores their packed codes and scales into every rank's output buffers (out_tbl[8 * i + r], i = lo_codes,
+  // lo_sf, hi_codes, hi_sf); nullptr = the plain form (all rows, own outputs)
+  uint8_t* const* out_tbl;
+  int row0;
   const uint4* gamma;    // bf16 [k] (RMSNorm weight) or nullptr
   float eps;
   int rows, k, k_lo;     // k_hi = k - k_lo
@@ -77,8 +82,19 @@ __device__ __forceinline__ float2 round_bf16_pair(const float2 y) {
   return make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
 }
 
-// Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued) that starts at element `o` of row
-// `row` (o < k_lo), stores its 16 bytes of codes when `ok`, and returns its two scale bytes (block order).
+// Output stores.  Plain: this rank's buffer.  Scattered tensor-parallel prologue: the same bytes into the buffer of
+// every rank (an all-gather by peer stores over NVLink).  `which` = 0 lo_codes, 1 lo_sf, 2 hi_codes, 3 hi_sf.
+template <typename T>
+__device__ __forceinline__ void store_out(const PackArgs& a, int which, uint8_t* own, size_t off, const T& val) {
+  if (a.out_tbl == nullptr) {
+    *reinterpret_cast<T*>(own + off) = val;
+  } else {
+    for (int r = 0; r < a.world; ++r) *reinterpret_cast<T*>(a.out_tbl[8 * which + r] + off) = val;
+  }
+}
+
+// Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued) that starts at element `o` of output
+// row `row` (o < k_lo), stores its 16 bytes of codes when `ok`, and returns its two scale bytes (block order).
 __device__ __forceinline__ uint32_t quantize_run_nvfp4(const PackArgs& a, const float2* v, int row, int o, bool ok) {
   uint32_t sf2 = 0;
   uint32_t words[4];
@@ -98,8 +114,7 @@ __device__ __forceinline__ uint32_t quantize_run_nvfp4(const PackArgs& a, const 
     sf2 |= c << (8 * b);
   }
   if (ok)
-    *reinterpret_cast<uint4*>(a.lo_codes + (static_cast<size_t>(row) * a.k_lo + o) / 2) =
-        make_uint4(words[0], words[1], words[2], words[3]);
+    store_out(a, 0, a.lo_codes, (static_cast<size_t>(row) * a.k_lo + o) / 2, make_uint4(words[0], words[1], words[2], words[3]));
   return sf2;
 }
 
@@ -116,13 +131,13 @@ __device__ __forceinline__ void quantize_run_mxfp8(const PackArgs& a, const floa
   const uint2 c0 = mxfp8_quantize8(v, inv), c1 = mxfp8_quantize8(v + 4, inv);
   const uint2 c2 = mxfp8_quantize8(v + 8, inv), c3 = mxfp8_quantize8(v + 12, inv);
   const int k_hi = a.k - a.k_lo, kh = o - a.k_lo;
-  uint4* dst = reinterpret_cast<uint4*>(a.hi_codes + static_cast<size_t>(row) * k_hi + kh);
-  dst[0] = make_uint4(c0.x, c0.y, c1.x, c1.y);
-  dst[1] = make_uint4(c2.x, c2.y, c3.x, c3.y);
+  const size_t coff = static_cast<size_t>(row) * k_hi + kh;
+  store_out(a, 2, a.hi_codes, coff, make_uint4(c0.x, c0.y, c1.x, c1.y));
+  store_out(a, 2, a.hi_codes, coff + 16, make_uint4(c2.x, c2.y, c3.x, c3.y));
   const int kb = kh >> 5;
   const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.hi_chunks))
                                 : static_cast<size_t>(row) * (k_hi >> 5) + kb;
-  a.hi_sf[off] = static_cast<uint8_t>(c);
+  store_out(a, 3, a.hi_sf, off, static_cast<uint8_t>(c));
 }
 
 // ---- staging through shared memory -------------------------------------------------------
@@ -365,7 +380,7 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
       if constexpr (PRO == 3) {
         // this warp's segment of x, summed over the ranks into the x slot (warp-local, like the copies)
         const int n = row_ok ? min(max(k8 - 256 * unit.seg, 0), 256) : 0;
-        const size_t off0 = static_cast<size_t>(row_ok ? row : 0) * k8 + 256 * unit.seg + lane;
+        const size_t off0 = static_cast<size_t>(row_ok ? row + a.row0 : 0) * k8 + 256 * unit.seg + lane;
         if (a.world <= 4) reduce_segment<4, 4>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
         else reduce_segment<2, 8>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
         __syncwarp();
@@ -496,16 +511,17 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     const int o0 = HAD ? 128 * (l >> 1) + 32 * p : 64 * l;
     const int o1 = HAD ? o0 + 64 : o0 + 32;
     uint32_t sf;
+    const int orow = PRO == 3 ? row + a.row0 : row;  // row of the outputs (the scattered prologue works on a slice)
     const bool hi0 = o0 >= a.k_lo && o0 < a.k, hi1 = o1 >= a.k_lo && o1 < a.k;
     if (!__any_sync(0xFFFFFFFFu, hi0 || hi1)) {     // the usual case: the whole warp is in the NVFP4 columns
-      sf = quantize_run_nvfp4(a, v, row, o0, row_ok && o0 < a.k_lo);
-      sf |= quantize_run_nvfp4(a, v + 16, row, o1, row_ok && o1 < a.k_lo) << 16;
+      sf = quantize_run_nvfp4(a, v, orow, o0, row_ok && o0 < a.k_lo);
+      sf |= quantize_run_nvfp4(a, v + 16, orow, o1, row_ok && o1 < a.k_lo) << 16;
     } else {                                         // a warp that holds MXFP8 columns
       sf = 0;
-      if (o0 < a.k_lo) sf = quantize_run_nvfp4(a, v, row, o0, row_ok);
-      else if (hi0 && row_ok) quantize_run_mxfp8(a, v, row, o0);
-      if (o1 < a.k_lo) sf |= quantize_run_nvfp4(a, v + 16, row, o1, row_ok) << 16;
-      else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, row, o1);
+      if (o0 < a.k_lo) sf = quantize_run_nvfp4(a, v, orow, o0, row_ok);
+      else if (hi0 && row_ok) quantize_run_mxfp8(a, v, orow, o0);
+      if (o1 < a.k_lo) sf |= quantize_run_nvfp4(a, v + 16, orow, o1, row_ok) << 16;
+      else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, orow, o1);
     }
     // NVFP4 scale bytes, one 32-bit word per 64 elements.  Plain rows: the lane's own four bytes.  Rotated rows:
     // the even lane has bytes 0,1 of both words of its block and the odd lane bytes 2,3: one exchange, one word each.
@@ -515,19 +531,41 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     }
     if (row_ok && 64 * l < a.k_lo) {
       const int kb = 4 * l;
-      const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.lo_chunks))
-                                    : static_cast<size_t>(row) * (a.k_lo >> 4) + kb;
-      *reinterpret_cast<uint32_t*>(a.lo_sf + off) = sf;
+      const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(orow, kb, a.lo_chunks))
+                                    : static_cast<size_t>(orow) * (a.k_lo >> 4) + kb;
+      store_out(a, 1, a.lo_sf, off, sf);
     }
   }
   cp_async_wait_all();
   if constexpr (PRO == 3) {
-    // the last block to finish closes the call: the counter the next call's handshake is derived from
+    // The last block to finish closes the call: the counter the next call's handshake is derived from.  In the
+    // scattered form it first tells every peer that this rank's rows are in place everywhere and waits (bounded)
+    // for the same word from all of them: when this grid completes, the rank's buffers hold every rank's rows
+    // and no peer reads this rank's partial sums any more.
+    if (a.out_tbl != nullptr) __threadfence_system();      // this thread's peer stores before the CTA's hand-in
     __syncthreads();
     if (tid == 0) {
       __threadfence();
       if (atomicAdd(a.sync + 1, 1) == static_cast<int>(gridDim.x) - 1) {
         a.sync[1] = 0;
+        if (a.out_tbl != nullptr) {
+          const int call = *reinterpret_cast<volatile int*>(a.sync) + 1;
+          __threadfence_system();
+          for (int r = 0; r < a.world; ++r)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flags[r] + 32 + a.rank), "r"(call) : "memory");
+          const long long t0 = clock64();
+          for (int r = 0; r < a.world; ++r) {
+            int seen;
+            do {
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(a.flags + 32 + r) : "memory");
+              if (seen - call >= 0) break;
+              if (clock64() - t0 > kWaitLimitCycles) {
+                atomicExch(a.status, PLQ_DEV_TIMEOUT);
+                break;
+              }
+            } while (true);
+          }
+        }
         __threadfence();
         atomicAdd(a.sync, 1);
       }
@@ -637,6 +675,8 @@ struct PeerArgs {
   int32_t* sync;
   int32_t* status;
   int world, rank, buffer_index;
+  uint8_t* const* out_tbl;   // scattered form: device array [32] of output addresses, see PackArgs
+  int row0;
 };
 
 static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int64_t ldx, const void* gamma, float eps,
@@ -661,12 +701,13 @@ static int launch_pack(int pro, const void* x, const void* x2, void* h_out, int6
   a.h_out = static_cast<uint4*>(h_out);
   a.ldx8 = static_cast<int>(ldx / 8);
   a.peer_x = nullptr; a.peer_flags = nullptr; a.flags = nullptr; a.sync = nullptr; a.status = nullptr;
-  a.world = 1; a.rank = 0; a.buffer_index = -1;
+  a.world = 1; a.rank = 0; a.buffer_index = -1; a.out_tbl = nullptr; a.row0 = 0;
   if (peers) {
     a.peer_x = reinterpret_cast<const uint4* const*>(peers->peer_x);
     a.peer_flags = reinterpret_cast<int* const*>(peers->peer_flags);
     a.flags = peers->flags; a.sync = peers->sync; a.status = peers->status;
     a.world = peers->world; a.rank = peers->rank; a.buffer_index = peers->buffer_index;
+    a.out_tbl = peers->out_tbl; a.row0 = peers->row0;
   }
   a.gamma = static_cast<const uint4*>(gamma);
   a.eps = eps;
@@ -797,7 +838,23 @@ extern "C" int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, voi
   if (!gamma_bf16) return PLQ_ERR_NULL;
   if (rows < 1) return PLQ_ERR_SHAPE;               // every rank must launch, or the others wait for it
   if (buffer_index < -1 || buffer_index > 1) return PLQ_ERR_SHAPE;
-  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank, buffer_index};
+  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank, buffer_index, nullptr, 0};
+  return plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
+                          lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
+}
+
+extern "C" int plq_reduce_scatter_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev,
+                                                   int32_t* flags, int32_t* sync, int world, int rank, int buffer_index,
+                                                   void* const* out_tbl_dev, int64_t row0, const void* residual_bf16,
+                                                   void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
+                                                   int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
+                                                   void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
+                                                   void* stream) {
+  if (!gamma_bf16 || !out_tbl_dev) return PLQ_ERR_NULL;
+  if (rows < 1 || row0 < 0 || row0 + rows > 0x7FFFFFFF) return PLQ_ERR_SHAPE;   // every rank must launch
+  if (buffer_index < -1 || buffer_index > 1) return PLQ_ERR_SHAPE;
+  const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank, buffer_index,
+                               reinterpret_cast<uint8_t* const*>(out_tbl_dev), static_cast<int>(row0)};
   return plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
                           lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
 }

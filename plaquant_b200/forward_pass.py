@@ -80,7 +80,8 @@ class ResQForwardB200:
 
     def __init__(self, cfg: LlamaConfig, device, ctx: Optional[tp.TPContext] = None, seed: int = 0,
                  num_layers: Optional[int] = None, fused_reduce_rows: int = 0, kv_quant: bool = False,
-                 weights: Optional[Dict[str, torch.Tensor]] = None, packed: Optional[dict] = None):
+                 weights: Optional[Dict[str, torch.Tensor]] = None, packed: Optional[dict] = None,
+                 scatter_prefill_rows: int = 0):
         """Weights come from one of three places: `packed` (the state a packed-weight container holds, see
         weight_packer.py), `weights` (a dict of full bf16 tensors under the reference's names, `l{i}.q_proj.weight`
         ... as `IndependentResQForward` takes them; every rank picks its own shard), or, with neither, a random
@@ -126,6 +127,11 @@ class ResQForwardB200:
         # decode batches of up to `fused_reduce_rows` rows reduce over peer memory inside the RMSNorm-quant kernel
         self.peer = (tp.PeerReduce(fused_reduce_rows, c.hidden_size, self.device, self.ctx.group)
                      if fused_reduce_rows > 0 and self.ctx.size > 1 else None)
+        # prefill batches of up to `scatter_prefill_rows` rows (B * T, a multiple of the number of ranks) keep the
+        # residual stream sharded by rows between the linears: reduce-scatter + norm + quantise + all-gather of the
+        # packed rows in one kernel over peer memory instead of an NCCL all-reduce of bf16
+        self.scatter = (tp.ScatterReduce(scatter_prefill_rows, c.hidden_size, self.k_hi_hidden, self.device, self.ctx.group)
+                        if scatter_prefill_rows > 0 and self.ctx.size > 1 else None)
 
     # ---- where the weights come from ---------------------------------------------------------------
     def _random_layer(self, li: int, seed: int) -> Dict[str, torch.Tensor]:
@@ -237,27 +243,11 @@ class ResQForwardB200:
             return (v.float() * cos + torch.cat([-v2, v1], -1).float() * sin).to(v.dtype)
         return rot(q), rot(k)
 
-    def _forward_layer(self, li: int, h: torch.Tensor, delta: Optional[torch.Tensor], pos0: int, cos_sin,
-                       static: Optional[dict] = None):
-        """One decoder layer.  `h` is the residual stream and `delta` the previous layer's MLP output that has
-        not been added to it yet (None for the first layer): the add is fused into this layer's first
-        RMSNorm-quant kernel, and the layer returns its own (h, delta) in the same form.
-
-        Without `static`, keys and values are kept in a growing Python-side cache (prefill, and decode steps of
-        arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...], the device tensors
-        `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position is data, which
-        is what CUDA-graph capture of a decode step needs."""
-        c, L = self.cfg, self.layers[li]
-        b, t, _ = h.shape
-        fused = self.peer is not None and b * t <= self.peer.rows      # all-reduce inside the RMSNorm-quant kernel
-        if delta is None:
-            qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
-        elif delta is _IN_PEER_BUFFER:   # h += sum over ranks of the previous down_proj; RMSNorm(ln1); quantise
-            h, pa = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, L.ln1, c.rms_eps, self.k_hi_hidden)
-            qkv = L.qkv(pa).view(b, t, -1)
-        else:   # h += delta; RMSNorm(ln1); rotate; quantise: one kernel
-            h, pa = ops.add_rmsnorm_pack(delta, h, L.ln1, c.rms_eps, self.k_hi_hidden)
-            qkv = L.qkv(pa).view(b, t, -1)
+    def _attention(self, li: int, qkv: torch.Tensor, pos0: int, cos_sin, static: Optional[dict]) -> torch.Tensor:
+        """[B, T, (heads + 2 kv_heads) * head_dim] fused projections -> RoPE -> cache update -> attention over the
+        cache -> [B, T, heads * head_dim] (this rank's heads)."""
+        c = self.cfg
+        b, t, _ = qkv.shape
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
         q, k = self._rope(q, k, cos_sin)
@@ -290,6 +280,30 @@ class ResQForwardB200:
             attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                   attn_mask=static["mask"], enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
+        return attn
+
+    def _forward_layer(self, li: int, h: torch.Tensor, delta: Optional[torch.Tensor], pos0: int, cos_sin,
+                       static: Optional[dict] = None):
+        """One decoder layer.  `h` is the residual stream and `delta` the previous layer's MLP output that has
+        not been added to it yet (None for the first layer): the add is fused into this layer's first
+        RMSNorm-quant kernel, and the layer returns its own (h, delta) in the same form.
+
+        Without `static`, keys and values are kept in a growing Python-side cache (prefill, and decode steps of
+        arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...], the device tensors
+        `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position is data, which
+        is what CUDA-graph capture of a decode step needs."""
+        c, L = self.cfg, self.layers[li]
+        b, t, _ = h.shape
+        fused = self.peer is not None and b * t <= self.peer.rows      # all-reduce inside the RMSNorm-quant kernel
+        if delta is None:
+            qkv = self._quantized_linear(h, L.qkv, norm_weight=L.ln1)
+        elif delta is _IN_PEER_BUFFER:   # h += sum over ranks of the previous down_proj; RMSNorm(ln1); quantise
+            h, pa = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, L.ln1, c.rms_eps, self.k_hi_hidden)
+            qkv = L.qkv(pa).view(b, t, -1)
+        else:   # h += delta; RMSNorm(ln1); rotate; quantise: one kernel
+            h, pa = ops.add_rmsnorm_pack(delta, h, L.ln1, c.rms_eps, self.k_hi_hidden)
+            qkv = L.qkv(pa).view(b, t, -1)
+        attn = self._attention(li, qkv, pos0, cos_sin, static)
         if fused:
             L.o(attn.reshape(b * t, -1), out=self.peer.buffer(b * t))                   # partial sums stay in the peer buffer
             h, pa = ops.allreduce_add_rmsnorm_pack(self.peer, b * t, h, L.ln2, c.rms_eps, self.k_hi_hidden)
@@ -318,6 +332,10 @@ class ResQForwardB200:
     def forward(self, input_ids: torch.Tensor, pos0: int = 0, all_positions: bool = False) -> torch.Tensor:
         """input_ids [B, T] -> logits of the last position [B, vocab] (float32), or of every position
         [B, T, vocab] with `all_positions` (what the reference's forward returns, forward_pass.py:178-183)."""
+        rows = input_ids.shape[0] * input_ids.shape[1]
+        if (self.scatter is not None and pos0 == 0 and rows <= self.scatter.rows and rows % self.ctx.size == 0
+                and rows > (self.peer.rows if self.peer is not None else 16)):
+            return self._prefill_scattered(input_ids, all_positions)
         if pos0 == 0:
             self.kv = [None] * len(self.layers)
         h = F.embedding(input_ids, self.embed)
@@ -329,6 +347,45 @@ class ResQForwardB200:
         self.pos = pos0 + input_ids.shape[1]
         h = self._finish(h, delta)
         return self._logits(h if all_positions else h[:, -1])
+
+    def _prefill_scattered(self, input_ids: torch.Tensor, all_positions: bool) -> torch.Tensor:
+        """Prefill with the residual stream sharded by rows (sequence-parallel between the linears).  Rank r keeps
+        rows [r * R / world, (r + 1) * R / world) of h; every row-parallel linear writes its partial output for all
+        R rows into the peer-visible buffer, and one kernel per norm reduces this rank's rows over NVLink, adds,
+        normalises, quantises, and stores the packed rows into every rank's packed buffer, which the next
+        column-parallel linear then reads whole.  Same arithmetic per row as the all-reduce path: the logits are
+        bit-identical."""
+        c, sr = self.cfg, self.scatter
+        b, t = input_ids.shape
+        R = b * t
+        per = R // self.ctx.size
+        self.kv = [None] * len(self.layers)
+        h_full = F.embedding(input_ids, self.embed).view(R, -1)
+        h = h_full[self.ctx.rank * per:(self.ctx.rank + 1) * per].contiguous()
+        cos_sin = self._rope_angles(torch.arange(0, t, device=h.device, dtype=torch.float32))
+        pa = ops.pack(h_full, self.k_hi_hidden, hadamard=True, gamma=self.layers[0].ln1, eps=c.rms_eps)
+        del h_full
+        for li, L in enumerate(self.layers):
+            if li > 0:      # h += previous down_proj (reduced over the ranks); RMSNorm(ln1); quantise; gather
+                h, pa = ops.reduce_scatter_add_rmsnorm_pack(sr, R, h, L.ln1, c.rms_eps)
+            attn = self._attention(li, L.qkv(pa).view(b, t, -1), 0, cos_sin, None)
+            L.o(attn.reshape(R, -1), out=sr.buffer(R))
+            h, pa = ops.reduce_scatter_add_rmsnorm_pack(sr, R, h, L.ln2, c.rms_eps)
+            pa = ops.silu_mul_pack(L.gate_up(pa), self.k_hi_ffn)
+            L.down(pa, out=sr.buffer(R))
+        h, _ = ops.reduce_scatter_add_rmsnorm_pack(sr, R, h, self.final_norm, c.rms_eps)     # last add; packed rows unused
+        self.pos = t
+        import torch.distributed as dist
+        if all_positions:
+            full = torch.empty(R, c.hidden_size, dtype=h.dtype, device=h.device)
+            dist.all_gather_into_tensor(full, h, group=self.ctx.group)
+            return self._logits(full.view(b, t, -1))
+        # only the last position of every sequence is needed: its owner contributes it, the others zeros
+        rows = torch.arange(b, device=h.device) * t + (t - 1) - self.ctx.rank * per
+        own = (rows >= 0) & (rows < per)
+        last = torch.where(own[:, None], h[rows.clamp(0, per - 1)].float(), torch.zeros((), device=h.device))
+        dist.all_reduce(last, group=self.ctx.group)            # one non-zero term per row: exact
+        return self._logits(last.to(h.dtype))
 
     def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
         """Final norm + unquantised LM head in the model dtype, for rows [..., hidden] (inference/forward_pass.py:178-181 in the reference)."""

@@ -188,6 +188,37 @@ def allreduce_add_rmsnorm_pack(peer, rows: int, residual: torch.Tensor, gamma: t
     return h.view(residual.shape), p
 
 
+def reduce_scatter_add_rmsnorm_pack(sr, rows_total: int, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
+                                    hadamard: bool = True):
+    """Scattered tensor-parallel add_rmsnorm_pack for prefill batches.  Every rank has written its partial output
+    [rows_total, k] of a row-parallel linear into `sr.buffer(rows_total)`; this rank sums its slice of
+    rows_total / world rows over the ranks, adds `residual` (its slice of the residual stream), normalises, rotates,
+    quantises, and stores the packed rows into every rank's packed buffer.  `sr` is a tp.ScatterReduce.  Returns
+    (h, packed): the new residual slice and the packed activations of ALL rows (complete when the kernel ends)."""
+    _require_cuda(residual, "residual")
+    k = residual.shape[-1]
+    r2 = residual.reshape(-1, k).contiguous()
+    if rows_total % sr.world != 0 or rows_total > sr.rows:
+        raise ValueError(f"{rows_total} rows do not split over {sr.world} ranks within buffers of {sr.rows} rows")
+    per = rows_total // sr.world
+    if r2.shape[0] != per or k != sr.k or residual.dtype != torch.bfloat16:
+        raise TypeError("residual must be this rank's bfloat16 [rows_total / world, k] slice")
+    if gamma.dtype != torch.bfloat16 or gamma.numel() != k:
+        raise TypeError("gamma must be bfloat16 [K]")
+    h = torch.empty_like(r2)
+    p = sr.packed(sr.next, rows_total)
+    with torch.cuda.device(residual.device):
+        st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
+            _ptr(sr.peer_x[sr.next]), _ptr(sr.peer_flags), _ptr(sr.flags), _ptr(sr.sync), sr.world, sr.rank, sr.next,
+            _ptr(sr.out_tbl[sr.next]), sr.rank * per, _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), per, k,
+            sr.k_hi, int(hadamard), _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), SF_TILED,
+            _ptr(status_word(residual.device)), _stream(residual.device))
+    _lib.check(st)
+    sr.next ^= 1
+    sr.calls += 1
+    return h, p
+
+
 def unpack(p: PackedMatrix) -> torch.Tensor:
     """Dequantise to bf16 [rows, K]: the value the reference's fake quantiser returns."""
     y = torch.empty(p.rows, p.k, dtype=torch.bfloat16, device=p.device)

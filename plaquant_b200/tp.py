@@ -110,3 +110,71 @@ class PeerReduce:
         """The [rows, k] view of the buffer the next fused reduction will read: the row-parallel linear writes
         its output here."""
         return self.x[self.next, :rows]
+
+
+class ScatterReduce:
+    """Peer-memory plumbing of the scattered form of the fused reduction (`ops.reduce_scatter_add_rmsnorm_pack`), the
+    prefill counterpart of `PeerReduce`: rank r sums rows [r * R / world, (r + 1) * R / world) of the ranks' partial
+    outputs, keeps the residual stream for those rows only, and stores their packed codes and scale bytes into the
+    packed-activation buffer of every rank (reduce-scatter in, all-gather of the 4.5-bit form out, both inside the
+    RMSNorm-quant kernel, by plain peer loads and stores).  Per rank: two symmetric bf16 [rows, k] buffer sets for
+    the partial outputs, two symmetric packed-activation sets (tiled scale layout), a symmetric flag array.
+
+    The sets alternate from call to call as in `PeerReduce`.  The kernel ends only after every rank has announced
+    that its rows are in place everywhere, so when a call has completed on a rank, that rank's packed buffer is
+    whole and no peer reads its partial sums of that call any more."""
+
+    def __init__(self, rows: int, k: int, k_hi: int, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        group = group if group is not None else dist.group.WORLD
+        self.rows, self.k, self.k_hi, self.device = rows, k, k_hi, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        k_lo = k - k_hi
+        L = _lib.lib()
+        al = lambda n: -(-n // 256) * 256
+        sizes = [rows * k_lo // 2, L.plq_sf_tiled_bytes(rows, k_lo // 16), rows * k_hi, L.plq_sf_tiled_bytes(rows, k_hi // 32)]
+        self._offsets = [0]
+        for n in sizes:
+            self._offsets.append(self._offsets[-1] + al(n))
+        self._sizes, per_set = sizes, self._offsets[-1]
+        self.x = symm_mem.empty(2, rows, k, dtype=torch.bfloat16, device=self.device)
+        self.out = symm_mem.empty(2, per_set, dtype=torch.uint8, device=self.device)
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=self.device)
+        self.out.zero_()
+        self.flags.zero_()
+        hx, ho, hf = (symm_mem.rendezvous(t, group) for t in (self.x, self.out, self.flags))
+        self._handles = (hx, ho, hf)
+        i64 = dict(dtype=torch.int64, device=self.device)
+        self.peer_x = [torch.tensor([int(p) + b * rows * k * 2 for p in hx.buffer_ptrs], **i64) for b in range(2)]
+        self.out_tbl = []
+        for b in range(2):
+            tbl = [0] * 32
+            for which in range(4):
+                for r, p in enumerate(ho.buffer_ptrs):
+                    tbl[8 * which + r] = int(p) + b * per_set + self._offsets[which]
+            self.out_tbl.append(torch.tensor(tbl, **i64))
+        self.peer_flags = torch.tensor([int(p) for p in hf.buffer_ptrs], **i64)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.next = 0
+        self.calls = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)
+
+    def buffer(self, rows: int) -> torch.Tensor:
+        """[rows, k] view of the partial-output buffer the next fused call reads."""
+        return self.x[self.next, :rows]
+
+    def packed(self, which: int, rows: int):
+        """PackedMatrix view of the first `rows` rows of packed-activation set `which`."""
+        from . import _lib, ops
+        k_lo, o, L = self.k - self.k_hi, self._offsets, _lib.lib()
+        buf = self.out[which]
+        return ops.PackedMatrix(
+            rows, k_lo, self.k_hi,
+            buf[o[0]:o[0] + rows * k_lo // 2].view(rows, k_lo // 2),
+            buf[o[1]:o[1] + L.plq_sf_tiled_bytes(rows, k_lo // 16)],
+            buf[o[2]:o[2] + rows * self.k_hi].view(rows, self.k_hi),
+            buf[o[3]:o[3] + L.plq_sf_tiled_bytes(rows, self.k_hi // 32)], ops.SF_TILED)

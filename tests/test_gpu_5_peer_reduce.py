@@ -218,3 +218,169 @@ def test_replayed_graph_alternates_buffer_sets_and_an_odd_call_count_is_reported
     with pytest.raises(plq.PlqError) as e:
         plq.check_device_status(dev)
     assert e.value.status == 2
+
+
+def _oracle_scatter(parts, res_full, gamma, k_hi):
+    """h = res + bf16(sum of parts in rank order), then RMSNorm + rotation + pack, for all rows."""
+    from oracle import formats as F
+    from tests._util import f32_of
+    acc = np.zeros(tuple(parts[0].shape), dtype=np.float32)
+    for part in parts:
+        acc = acc + f32_of(part)
+    want_h = F.add_bf16(f32_of(res_full), F.round_to_bf16(acc))
+    return want_h, F.prepare_activation(want_h, k_hi, gamma=f32_of(gamma), eps=1e-6, hadamard=True)
+
+
+@pytest.mark.parametrize("world,total,k,k_hi", [(2, 6, 1024, 64), (4, 264, 4096, 128), (8, 16, 2048, 64)])
+def test_scattered_form_with_emulated_ranks_on_one_gpu(world, total, k, k_hi):
+    """Reduce-scatter + add + RMSNorm-quant + all-gather of the packed rows, `world` ranks emulated on one GPU one
+    after the other: every rank has its own flag array and its own packed output buffers on this GPU, the other
+    ranks' announcements (start and completion words) are written from the host before a rank runs.  After all
+    ranks have run, EVERY rank's packed buffer must hold all rows, bit-exact against the CPU restatement, and the
+    residual slices must tile the full residual stream."""
+    from oracle import formats as F
+    from plaquant_b200 import _lib, ops
+    from tests._util import f32_of, packed_to_numpy, synth_activation, synth_gamma
+    dev = torch.device("cuda", 0)
+    per = total // world
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
+    sync = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(world)]
+    peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+    outs = [ops.alloc_packed(total, k, k_hi, "tiled", dev) for _ in range(world)]
+    tbl = [0] * 32
+    for r, o in enumerate(outs):
+        for i, t in enumerate((o.lo_codes, o.lo_sf, o.hi_codes, o.hi_sf)):
+            tbl[8 * i + r] = t.data_ptr()
+    tbl_d = torch.tensor(tbl, dtype=torch.int64, device=dev)
+    gamma = synth_gamma(k, 3)
+    gamma_d = gamma.cuda()
+    for call in (1, 2):
+        parts = [synth_activation(total, k, seed=50 * call + r) for r in range(world)]
+        parts_d = [p.cuda() for p in parts]
+        res = synth_activation(total, k, seed=50 * call + 40)
+        res_d = res.cuda()
+        peer_x = torch.tensor([p.data_ptr() for p in parts_d], dtype=torch.int64, device=dev)
+        h = torch.zeros(total, k, dtype=torch.bfloat16, device=dev)
+        for r in range(world):
+            for j in range(world):
+                if j != r:                      # "rank j has announced this call and its completion" (kept if already ahead)
+                    flags[r][j] = call
+                    flags[r][32 + j] = call
+            st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
+                peer_x.data_ptr(), peer_flags.data_ptr(), flags[r].data_ptr(), sync[r].data_ptr(), world, r, -1,
+                tbl_d.data_ptr(), r * per, res_d[r * per:].data_ptr(), h[r * per:].data_ptr(), gamma_d.data_ptr(), 1e-6,
+                per, k, k_hi, 1, outs[r].lo_codes.data_ptr(), outs[r].lo_sf.data_ptr(), outs[r].hi_codes.data_ptr(),
+                outs[r].hi_sf.data_ptr(), 1, ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            assert st == 0
+            plq.check_device_status(dev)
+            assert int(sync[r][0].item()) == call
+        for r in range(world):                  # every rank told every other one, start and completion
+            f = flags[r].cpu().numpy()
+            assert (f[:world] == call).all() and (f[32:32 + world] == call).all()
+        want_h, want = _oracle_scatter(parts, res, gamma, k_hi)
+        assert np.array_equal(f32_of(h), want_h)
+        for o in outs:
+            got = packed_to_numpy(o)
+            for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
+                assert np.array_equal(got[key], want[key]), key
+
+
+def test_scattered_form_times_out_when_a_peer_never_completes():
+    """Rank 1 announces the call but never its completion: the closing wait is bounded, the kernel stores
+    PLQ_DEV_TIMEOUT and ends, and the context stays usable."""
+    from plaquant_b200 import _lib, ops
+    from tests._util import synth_activation, synth_gamma
+    dev = torch.device("cuda", 0)
+    total, k, k_hi, world = 4, 1024, 64, 2
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    other = torch.zeros(64, dtype=torch.int32, device=dev)
+    sync = torch.zeros(2, dtype=torch.int32, device=dev)
+    flags[1] = 1                                   # started, but flags[33] stays 0
+    peer_flags = torch.tensor([flags.data_ptr(), other.data_ptr()], dtype=torch.int64, device=dev)
+    x = synth_activation(total, k, seed=5).cuda()
+    peer_x = torch.tensor([x.data_ptr()] * 2, dtype=torch.int64, device=dev)
+    outs = [ops.alloc_packed(total, k, k_hi, "tiled", dev) for _ in range(2)]
+    tbl = [0] * 32
+    for r, o in enumerate(outs):
+        for i, t in enumerate((o.lo_codes, o.lo_sf, o.hi_codes, o.hi_sf)):
+            tbl[8 * i + r] = t.data_ptr()
+    tbl_d = torch.tensor(tbl, dtype=torch.int64, device=dev)
+    gamma = synth_gamma(k, 2).cuda()
+    h = torch.empty(2, k, dtype=torch.bfloat16, device=dev)
+    st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
+        peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, 0, tbl_d.data_ptr(), 0,
+        x.data_ptr(), h.data_ptr(), gamma.data_ptr(), 1e-6, 2, k, k_hi, 1, outs[0].lo_codes.data_ptr(),
+        outs[0].lo_sf.data_ptr(), outs[0].hi_codes.data_ptr(), outs[0].hi_sf.data_ptr(), 1,
+        ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    assert st == 0
+    with pytest.raises(plq.PlqError) as e:
+        plq.check_device_status(dev)
+    assert e.value.status == 1
+    assert int(sync[0].item()) == 1 and int(other[32].item()) == 1
+    plq.pack(x, k_hi, hadamard=True)
+    plq.check_device_status(dev)
+
+
+def _scatter_worker(rank, world, port, total, k, k_hi, calls, q):
+    try:
+        import torch.distributed as dist
+        from plaquant_b200 import ops, tp
+        from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+        from tests._util import f32_of, packed_to_numpy
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        sr = tp.ScatterReduce(total, k, k_hi, dev)
+        per = total // world
+        g = torch.Generator().manual_seed(11)
+        gamma = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
+        ok = True
+        for c in range(calls):
+            parts = [torch.randn(total, k, generator=g).to(torch.bfloat16) for _ in range(world)]
+            res = torch.randn(total, k, generator=g).to(torch.bfloat16)
+            sr.buffer(total).copy_(parts[rank].to(dev))
+            h, p = ops.reduce_scatter_add_rmsnorm_pack(sr, total, res[rank * per:(rank + 1) * per].to(dev), gamma.to(dev), 1e-6)
+            plq.check_device_status(dev)
+            want_h, want = _oracle_scatter(parts, res, gamma, k_hi)
+            got = packed_to_numpy(p)
+            ok = ok and np.array_equal(f32_of(h), want_h[rank * per:(rank + 1) * per])
+            ok = ok and all(np.array_equal(got[key], want[key]) for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"))
+        # the decoder: prefill with the row-sharded residual stream gives the logits of the all-reduce path, bit for bit
+        cfg = LlamaConfig(hidden_size=1024, intermediate_size=1024 * world, num_layers=2, num_heads=8 * world,
+                          num_kv_heads=world, head_dim=128, vocab_size=512)
+        ctx = tp.TPContext(rank, world, None)
+        ids = torch.randint(0, cfg.vocab_size, (2, 16 * world), generator=torch.Generator().manual_seed(3)).to(dev)
+        plain = ResQForwardB200(cfg, dev, ctx, seed=5)
+        a = plain.forward(ids)
+        sharded = ResQForwardB200(cfg, dev, ctx, seed=5, scatter_prefill_rows=ids.numel())
+        b = sharded.forward(ids)
+        b_all = sharded.forward(ids, all_positions=True)
+        plq.check_device_status(dev)
+        ok_model = sharded.scatter.calls == 4 * len(sharded.layers) and torch.equal(a, b) and \
+            torch.equal(b_all[:, -1], a) and \
+            all(torch.equal(x, y) for kv0, kv1 in zip(plain.kv, sharded.kv) for x, y in zip(kv0, kv1))
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, bool(ok and ok_model), "" if ok_model else "model mismatch"))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        q.put((rank, False, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("total,k,k_hi", [(256, 4096, 128), (8, 1024, 64)])
+def test_scattered_form_across_gpus_bit_exact(total, k, k_hi):
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_scatter_worker, args=(r, world, port, total, k, k_hi, 4, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
