@@ -135,14 +135,16 @@ class ResQForwardB200:
 
     # ---- where the weights come from ---------------------------------------------------------------
     def _random_layer(self, li: int, seed: int) -> Dict[str, torch.Tensor]:
-        """This rank's bf16 tensors of layer `li`: norm weights ~ U(0.5, 1.5), linears ~ N(0, 0.02)."""
+        """This rank's bf16 tensors of layer `li`: norm weights ~ U(0.5, 1.5) (replicated: the same on every rank,
+        from a stream of their own), linears ~ N(0, 0.02) (this rank's shards)."""
         c, r = self.cfg, self.ctx.rank
         g = torch.Generator(device=self.device).manual_seed(seed * 100003 + li * 16 + r)
+        gn = torch.Generator(device=self.device).manual_seed(seed * 100003 + li * 16 + 15)
 
         def lin(n, k):
             return (torch.randn(n, k, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
-        t = {"ln1": (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16),
-             "ln2": (torch.rand(c.hidden_size, generator=g, device=self.device) + 0.5).to(torch.bfloat16)}
+        t = {"ln1": (torch.rand(c.hidden_size, generator=gn, device=self.device) + 0.5).to(torch.bfloat16),
+             "ln2": (torch.rand(c.hidden_size, generator=gn, device=self.device) + 0.5).to(torch.bfloat16)}
         t["qkv"] = lin((self.heads + 2 * self.kv_heads) * c.head_dim, c.hidden_size)
         t["o"] = lin(c.hidden_size, self.heads * c.head_dim)
         t["gate_up"] = lin(2 * self.ffn, c.hidden_size)

@@ -354,16 +354,18 @@ def _scatter_worker(rank, world, port, total, k, k_hi, calls, q):
         ids = torch.randint(0, cfg.vocab_size, (2, 16 * world), generator=torch.Generator().manual_seed(3)).to(dev)
         plain = ResQForwardB200(cfg, dev, ctx, seed=5)
         a = plain.forward(ids)
+        a_all = plain.forward(ids, all_positions=True)
         sharded = ResQForwardB200(cfg, dev, ctx, seed=5, scatter_prefill_rows=ids.numel())
         b = sharded.forward(ids)
         b_all = sharded.forward(ids, all_positions=True)
         plq.check_device_status(dev)
-        ok_model = sharded.scatter.calls == 4 * len(sharded.layers) and torch.equal(a, b) and \
-            torch.equal(b_all[:, -1], a) and \
-            all(torch.equal(x, y) for kv0, kv1 in zip(plain.kv, sharded.kv) for x, y in zip(kv0, kv1))
+        checks = {"calls": sharded.scatter.calls == 4 * len(sharded.layers), "last": torch.equal(a, b),
+                  "all": torch.equal(a_all, b_all),
+                  "kv": all(torch.equal(x, y) for kv0, kv1 in zip(plain.kv, sharded.kv) for x, y in zip(kv0, kv1))}
+        ok_model = all(checks.values())
         dist.barrier()
         dist.destroy_process_group()
-        q.put((rank, bool(ok and ok_model), "" if ok_model else "model mismatch"))
+        q.put((rank, bool(ok and ok_model), "" if ok_model else f"model mismatch: {checks}"))
     except Exception as exc:  # noqa: BLE001
         import traceback
         q.put((rank, False, traceback.format_exc()))
