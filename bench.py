@@ -576,8 +576,10 @@ def main_model(args, rank, local_rank, world):
     ctx = tp.TPContext(rank, world, None)
     cfg = LlamaConfig.llama3_70b()
     layers = args.layers or cfg.num_layers
-    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0)
     batch, prefill, decode = args.batch, args.prefill, args.decode
+    scattered = args.fused_reduce and args.scatter_prefill and world > 1 and (batch * prefill) % world == 0
+    model = ResQForwardB200(cfg, dev, ctx, seed=4, num_layers=layers, fused_reduce_rows=16 if args.fused_reduce else 0,
+                            scatter_prefill_rows=batch * prefill if scattered else 0)
     ids = torch.randint(0, cfg.vocab_size, (batch, prefill), generator=torch.Generator().manual_seed(40)).to(dev)
 
     def run():
@@ -625,7 +627,8 @@ def main_model(args, rank, local_rank, world):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4+mxfp8 (f32 accumulate)",
             "data": "synthetic", "clocks": clocks, "ranks_agree_on_tokens": same, "last_run_phases": phases,
             "config": {"workload": f"Llama-3-70B architecture, {layers} of 80 layers, random init, batch {batch}, "
-                                   f"prefill {prefill} + {decode} greedy decode steps", "parallelism": f"tp{world}"}}),
+                                   f"prefill {prefill} + {decode} greedy decode steps", "parallelism": f"tp{world}",
+                       "prefill_reduce": "fused reduce-scatter / all-gather" if scattered else ("NCCL" if world > 1 else "none")}}),
             flush=True)
     if world > 1:
         dist.destroy_process_group()

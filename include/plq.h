@@ -156,29 +156,34 @@ PLQ_API int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, void* 
  * Scattered form of plq_allreduce_add_rmsnorm_pack for prefill batches (sequence-parallel between the row-parallel
  * linear and the next column-parallel one): a reduce-scatter of the partial outputs, the residual add and RMSNorm
  * on this rank's rows only, and an all-gather of the PACKED rows (4.5 bits per element instead of 16) in one
- * kernel.  The ranks' partial outputs are bf16 [total, k]; this rank handles rows [row0, row0 + rows).
- *   peer_x_dev       as above, the buffers being [total, k]
+ * kernel.  The ranks' partial outputs are bf16 [total_rows, k]; this rank handles rows [row0, row0 + rows).
+ *   peer_x_dev       as above, the buffers being [total_rows, k]
  *   out_tbl_dev      device array [32] of addresses: entry 8 * i + r is rank r's buffer of output i (0 lo_codes
- *                    [total, k_lo/2], 1 lo_sf, 2 hi_codes [total, k_hi], 3 hi_sf); the rows are stored at their
- *                    global row index into every rank's buffers by peer stores
+ *                    [total_rows, k_lo/2], 1 lo_sf ROW-MAJOR [total_rows, k_lo/16], 2 hi_codes [total_rows, k_hi],
+ *                    3 hi_sf ROW-MAJOR [total_rows, k_hi/32]); the rows are stored at their global row index into
+ *                    every rank's buffers by peer stores, whole 128-byte lines per warp
  *   residual, h_out  this rank's slice [rows, k] of the residual stream (local memory)
- *   lo_codes .. hi_sf  this rank's own output buffers (the addresses in column `rank` of the table)
+ *   lo_codes, lo_sf_rowmajor, hi_codes, hi_sf_rowmajor   this rank's own buffers (column `rank` of the table)
+ *   lo_sf_tiled, hi_sf_tiled   local buffers of plq_sf_tiled_bytes(total_rows, ...) bytes, or both NULL: when
+ *                    given, a second small kernel rewrites the gathered scale bytes of ALL rows into the tiled
+ *                    layout the GEMM reads (padding written as zero)
  *   flags            int32 [64]: words [0, world) announce a call, words [32, 32 + world) its completion
- * The kernel completes only after every rank has stored its rows everywhere and said so (bounded wait,
- * PLQ_DEV_TIMEOUT otherwise): on return of the stream to the caller the packed buffers hold all `total` rows
- * and no peer reads this rank's partial outputs of this call any more.  Call sequence, buffer alternation and
- * `buffer_index` as for plq_allreduce_add_rmsnorm_pack (the packed output buffers alternate together with the
- * partial-output buffers).  Every rank must call with rows >= 1.
+ * The first kernel completes only after every rank has stored its rows everywhere and said so (bounded wait,
+ * PLQ_DEV_TIMEOUT otherwise): when the call's work has completed on the stream, the packed buffers hold all
+ * `total_rows` rows and no peer reads this rank's partial outputs of this call any more.  Call sequence, buffer
+ * alternation and `buffer_index` as for plq_allreduce_add_rmsnorm_pack (the output buffers alternate together
+ * with the partial-output buffers).  Every rank must call with rows >= 1.
  * Replaces `dist.all_reduce` + residual add + rms_norm + quantiser for prefill batches of a tensor-parallel
  * decoder layer (inference/forward_pass.py:258-264 under tensor parallelism); the reference has no such step.
  */
 PLQ_API int plq_reduce_scatter_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev,
                                                 int32_t* flags, int32_t* sync, int world, int rank, int buffer_index,
-                                                void* const* out_tbl_dev, int64_t row0, const void* residual_bf16,
-                                                void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
-                                                int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
-                                                void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
-                                                void* stream);
+                                                void* const* out_tbl_dev, int64_t row0, int64_t total_rows,
+                                                const void* residual_bf16, void* h_out_bf16, const void* gamma_bf16,
+                                                float eps, int64_t rows, int64_t k, int64_t k_hi, int hadamard,
+                                                void* lo_codes, void* lo_sf_rowmajor, void* hi_codes,
+                                                void* hi_sf_rowmajor, void* lo_sf_tiled, void* hi_sf_tiled,
+                                                int32_t* dev_status, void* stream);
 
 /*
  * One column block of GPTQ for the block-scaled formats: columns [col0, col0 + count), count <= 128, of the

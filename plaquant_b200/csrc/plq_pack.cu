@@ -93,9 +93,9 @@ __device__ __forceinline__ void store_out(const PackArgs& a, int which, uint8_t*
   }
 }
 
-// Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued) that starts at element `o` of output
-// row `row` (o < k_lo), stores its 16 bytes of codes when `ok`, and returns its two scale bytes (block order).
-__device__ __forceinline__ uint32_t quantize_run_nvfp4(const PackArgs& a, const float2* v, int row, int o, bool ok) {
+// Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued): its 16 bytes of codes go to `codes`,
+// its two scale bytes (block order) are returned.
+__device__ __forceinline__ uint32_t quantize_run_nvfp4(const float2* v, uint4& codes) {
   uint32_t sf2 = 0;
   uint32_t words[4];
 #pragma unroll
@@ -113,9 +113,13 @@ __device__ __forceinline__ uint32_t quantize_run_nvfp4(const PackArgs& a, const 
     words[2 * b + 1] = nvfp4_quantize8(v + 8 * b + 4, s, r);
     sf2 |= c << (8 * b);
   }
-  if (ok)
-    store_out(a, 0, a.lo_codes, (static_cast<size_t>(row) * a.k_lo + o) / 2, make_uint4(words[0], words[1], words[2], words[3]));
+  codes = make_uint4(words[0], words[1], words[2], words[3]);
   return sf2;
+}
+
+// Codes of the run that starts at element `o` of output row `row` (o < k_lo).
+__device__ __forceinline__ void store_run_nvfp4(const PackArgs& a, const uint4& codes, int row, int o) {
+  store_out(a, 0, a.lo_codes, (static_cast<size_t>(row) * a.k_lo + o) / 2, codes);
 }
 
 // The same for a run in the MXFP8 columns (o >= k_lo): 32 code bytes and one scale byte.
@@ -370,6 +374,7 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     // v[16 r + 4 c + i] holds elements (8 c + 2 i, 8 c + 2 i + 1) of register run r.  Arithmetic on pairs uses the
     // packed float32x2 instructions of sm_100 (same IEEE rounding per element, half the issue slots).
     float2 v[32];
+    int cur_slot;
 
     // ---- this group's pieces: shared memory -> registers; then the next group's copies start ----------
     {
@@ -381,8 +386,9 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
         // this warp's segment of x, summed over the ranks into the x slot (warp-local, like the copies)
         const int n = row_ok ? min(max(k8 - 256 * unit.seg, 0), 256) : 0;
         const size_t off0 = static_cast<size_t>(row_ok ? row + a.row0 : 0) * k8 + 256 * unit.seg + lane;
-        if (a.world <= 4) reduce_segment<4, 4>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
-        else reduce_segment<2, 8>(xs0 + slot * stage_bytes, a.peer_x, a.world, off0, n, lane);
+        const uint4* const* px = a.peer_x;
+        if (a.world <= 4) reduce_segment<4, 4>(xs0 + slot * stage_bytes, px, a.world, off0, n, lane);
+        else reduce_segment<2, 8>(xs0 + slot * stage_bytes, px, a.world, off0, n, lane);
         __syncwarp();
       }
       if constexpr (kStageX) read_line(xs0 + slot * stage_bytes, lane, xr, w);
@@ -390,6 +396,7 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
       __syncwarp();                                 // every lane has its pieces: the slot is free again
       if (group + a.stages * stride < ngroups) stage_group(group + a.stages * stride, slot);
       cp_async_commit();
+      cur_slot = slot;
       if (++slot == a.stages) slot = 0;
       if constexpr (PRO == 0) {
 #pragma unroll
@@ -513,15 +520,50 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     uint32_t sf;
     const int orow = PRO == 3 ? row + a.row0 : row;  // row of the outputs (the scattered prologue works on a slice)
     const bool hi0 = o0 >= a.k_lo && o0 < a.k, hi1 = o1 >= a.k_lo && o1 < a.k;
+    uint4 c0, c1;
     if (!__any_sync(0xFFFFFFFFu, hi0 || hi1)) {     // the usual case: the whole warp is in the NVFP4 columns
-      sf = quantize_run_nvfp4(a, v, orow, o0, row_ok && o0 < a.k_lo);
-      sf |= quantize_run_nvfp4(a, v + 16, orow, o1, row_ok && o1 < a.k_lo) << 16;
+      sf = quantize_run_nvfp4(v, c0);
+      sf |= quantize_run_nvfp4(v + 16, c1) << 16;
+      bool direct = true;
+      if constexpr (PRO == 3) {
+        if (a.out_tbl != nullptr) {
+          // Scattered form: the warp's 1 KB of codes goes to every rank.  Each lane holds two 16-byte pieces that
+          // are not neighbours of the next lane's; they pass through the warp's (now free) x slot so that one
+          // store instruction covers 512 consecutive bytes - whole lines over NVLink instead of half sectors.
+          direct = false;
+          uint8_t* sc = xs0 + cur_slot * stage_bytes;
+          const int seg0 = 2048 * unit.seg;
+          const int q0 = (o0 - seg0) >> 5, q1 = (o1 - seg0) >> 5;           // piece index inside the segment
+          *reinterpret_cast<uint4*>(sc + 16 * (q0 ^ ((q0 >> 2) & 2))) = c0;
+          *reinterpret_cast<uint4*>(sc + 16 * (q1 ^ ((q1 >> 2) & 2))) = c1;
+          __syncwarp();
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int q = 32 * half + lane;
+            const uint4 val = *reinterpret_cast<const uint4*>(sc + 16 * (q ^ ((q >> 2) & 2)));
+            const int o = seg0 + 32 * q;
+            if (row_ok && o < a.k_lo) {
+              const size_t off = (static_cast<size_t>(orow) * a.k_lo + o) / 2;
+              for (int r = 0; r < a.world; ++r) *reinterpret_cast<uint4*>(a.out_tbl[r] + off) = val;
+            }
+          }
+          __syncwarp();                                // the slot is summed into again only after this
+        }
+      }
+      if (direct) {
+        if (row_ok && o0 < a.k_lo) store_run_nvfp4(a, c0, orow, o0);
+        if (row_ok && o1 < a.k_lo) store_run_nvfp4(a, c1, orow, o1);
+      }
     } else {                                         // a warp that holds MXFP8 columns
       sf = 0;
-      if (o0 < a.k_lo) sf = quantize_run_nvfp4(a, v, orow, o0, row_ok);
-      else if (hi0 && row_ok) quantize_run_mxfp8(a, v, orow, o0);
-      if (o1 < a.k_lo) sf |= quantize_run_nvfp4(a, v + 16, orow, o1, row_ok) << 16;
-      else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, orow, o1);
+      if (o0 < a.k_lo) {
+        sf = quantize_run_nvfp4(v, c0);
+        if (row_ok) store_run_nvfp4(a, c0, orow, o0);
+      } else if (hi0 && row_ok) quantize_run_mxfp8(a, v, orow, o0);
+      if (o1 < a.k_lo) {
+        sf |= quantize_run_nvfp4(v + 16, c1) << 16;
+        if (row_ok) store_run_nvfp4(a, c1, orow, o1);
+      } else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, orow, o1);
     }
     // NVFP4 scale bytes, one 32-bit word per 64 elements.  Plain rows: the lane's own four bytes.  Rotated rows:
     // the even lane has bytes 0,1 of both words of its block and the odd lane bytes 2,3: one exchange, one word each.
@@ -843,20 +885,64 @@ extern "C" int plq_allreduce_add_rmsnorm_pack(const void* const* peer_x_dev, voi
                           lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
 }
 
+namespace plq {
+// Row-major scale bytes [rows, n_sf] -> the tiled layout the GEMM reads, one 32-bit word (four scales of one row)
+// per thread, consecutive threads writing consecutive words of a 512-byte chunk.  Scales beyond n_sf and rows beyond
+// `rows` inside the last 128-row group are written as zero.
+__global__ void __launch_bounds__(256) tile_sf_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                      int rows, int n_sf, int chunks, long long words) {
+  const long long w = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (w >= words) return;
+  const int in_chunk = static_cast<int>(w & 127);             // (r & 31) * 4 + ((r >> 5) & 3)
+  const long long chunk_id = w >> 7;                           // (r >> 7) * chunks + kb / 4
+  const int c = static_cast<int>(chunk_id % chunks);
+  const int r = static_cast<int>(chunk_id / chunks) * 128 + (in_chunk & 3) * 32 + (in_chunk >> 2);
+  uint32_t v = 0;
+  if (r < rows) {
+    const uint8_t* p = src + static_cast<size_t>(r) * n_sf + 4 * c;
+    if (4 * c + 4 <= n_sf && (n_sf & 3) == 0) v = *reinterpret_cast<const uint32_t*>(p);
+    else
+      for (int i = 0; i < 4 && 4 * c + i < n_sf; ++i) v |= static_cast<uint32_t>(p[i]) << (8 * i);
+  }
+  reinterpret_cast<uint32_t*>(dst)[w] = v;
+}
+
+static int launch_tile_sf(const void* src, void* dst, int64_t rows, int64_t n_sf, cudaStream_t stream) {
+  if (n_sf == 0) return PLQ_OK;
+  const int64_t chunks = (n_sf + 3) / 4;
+  const long long words = ((rows + 127) / 128) * chunks * 128;
+  tile_sf_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), static_cast<int>(rows), static_cast<int>(n_sf),
+      static_cast<int>(chunks), words);
+  return cudaGetLastError() == cudaSuccess ? PLQ_OK : PLQ_ERR_CUDA;
+}
+}  // namespace plq
+
 extern "C" int plq_reduce_scatter_add_rmsnorm_pack(const void* const* peer_x_dev, void* const* peer_flags_dev,
                                                    int32_t* flags, int32_t* sync, int world, int rank, int buffer_index,
-                                                   void* const* out_tbl_dev, int64_t row0, const void* residual_bf16,
-                                                   void* h_out_bf16, const void* gamma_bf16, float eps, int64_t rows,
-                                                   int64_t k, int64_t k_hi, int hadamard, void* lo_codes, void* lo_sf,
-                                                   void* hi_codes, void* hi_sf, int sf_layout, int32_t* dev_status,
-                                                   void* stream) {
+                                                   void* const* out_tbl_dev, int64_t row0, int64_t total_rows,
+                                                   const void* residual_bf16, void* h_out_bf16, const void* gamma_bf16,
+                                                   float eps, int64_t rows, int64_t k, int64_t k_hi, int hadamard,
+                                                   void* lo_codes, void* lo_sf_rowmajor, void* hi_codes,
+                                                   void* hi_sf_rowmajor, void* lo_sf_tiled, void* hi_sf_tiled,
+                                                   int32_t* dev_status, void* stream) {
   if (!gamma_bf16 || !out_tbl_dev) return PLQ_ERR_NULL;
-  if (rows < 1 || row0 < 0 || row0 + rows > 0x7FFFFFFF) return PLQ_ERR_SHAPE;   // every rank must launch
+  if (rows < 1 || row0 < 0 || row0 + rows > total_rows || total_rows > 0x7FFFFFFF) return PLQ_ERR_SHAPE;
   if (buffer_index < -1 || buffer_index > 1) return PLQ_ERR_SHAPE;
+  if ((lo_sf_tiled != nullptr) != (hi_sf_tiled != nullptr || k_hi == 0)) return PLQ_ERR_NULL;
+  if (lo_sf_tiled && ((reinterpret_cast<uintptr_t>(lo_sf_tiled) | reinterpret_cast<uintptr_t>(hi_sf_tiled)) & 15))
+    return PLQ_ERR_ALIGN;
   const plq::PeerArgs peers = {peer_x_dev, peer_flags_dev, flags, sync, dev_status, world, rank, buffer_index,
                                reinterpret_cast<uint8_t* const*>(out_tbl_dev), static_cast<int>(row0)};
-  return plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
-                          lo_sf, hi_codes, hi_sf, sf_layout, stream, &peers);
+  // the kernel gathers the scale bytes row-major (whole lines per warp over NVLink); the GEMM's tiled copy is
+  // made locally afterwards, for all rows, once the kernel has seen every rank finish
+  int st = plq::launch_pack(3, nullptr, residual_bf16, h_out_bf16, k, gamma_bf16, eps, rows, k, k_hi, hadamard, lo_codes,
+                            lo_sf_rowmajor, hi_codes, hi_sf_rowmajor, PLQ_SF_ROWMAJOR, stream, &peers);
+  if (st != PLQ_OK || !lo_sf_tiled) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  st = plq::launch_tile_sf(lo_sf_rowmajor, lo_sf_tiled, total_rows, (k - k_hi) / 16, cs);
+  if (st == PLQ_OK) st = plq::launch_tile_sf(hi_sf_rowmajor, hi_sf_tiled, total_rows, k_hi / 32, cs);
+  return st;
 }
 
 extern "C" int plq_unpack(const void* lo_codes, const void* lo_sf, const void* hi_codes, const void* hi_sf,

@@ -206,13 +206,13 @@ def reduce_scatter_add_rmsnorm_pack(sr, rows_total: int, residual: torch.Tensor,
     if gamma.dtype != torch.bfloat16 or gamma.numel() != k:
         raise TypeError("gamma must be bfloat16 [K]")
     h = torch.empty_like(r2)
-    p = sr.packed(sr.next, rows_total)
+    p, lo_rm, hi_rm = sr.packed(sr.next, rows_total)
     with torch.cuda.device(residual.device):
         st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
             _ptr(sr.peer_x[sr.next]), _ptr(sr.peer_flags), _ptr(sr.flags), _ptr(sr.sync), sr.world, sr.rank, sr.next,
-            _ptr(sr.out_tbl[sr.next]), sr.rank * per, _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps), per, k,
-            sr.k_hi, int(hadamard), _ptr(p.lo_codes), _ptr(p.lo_sf), _ptr(p.hi_codes), _ptr(p.hi_sf), SF_TILED,
-            _ptr(status_word(residual.device)), _stream(residual.device))
+            _ptr(sr.out_tbl[sr.next]), sr.rank * per, rows_total, _ptr(r2), _ptr(h), _ptr(gamma.contiguous()), float(eps),
+            per, k, sr.k_hi, int(hadamard), _ptr(p.lo_codes), _ptr(lo_rm), _ptr(p.hi_codes), _ptr(hi_rm),
+            _ptr(p.lo_sf), _ptr(p.hi_sf), _ptr(status_word(residual.device)), _stream(residual.device))
     _lib.check(st)
     sr.next ^= 1
     sr.calls += 1

@@ -118,7 +118,8 @@ class ScatterReduce:
     outputs, keeps the residual stream for those rows only, and stores their packed codes and scale bytes into the
     packed-activation buffer of every rank (reduce-scatter in, all-gather of the 4.5-bit form out, both inside the
     RMSNorm-quant kernel, by plain peer loads and stores).  Per rank: two symmetric bf16 [rows, k] buffer sets for
-    the partial outputs, two symmetric packed-activation sets (tiled scale layout), a symmetric flag array.
+    the partial outputs, two symmetric packed-activation sets (codes, and scale bytes row-major), a symmetric flag
+    array, and two local sets of tiled scale buffers that the call fills from the gathered row-major ones.
 
     The sets alternate from call to call as in `PeerReduce`.  The kernel ends only after every rank has announced
     that its rows are in place everywhere, so when a call has completed on a rank, that rank's packed buffer is
@@ -135,7 +136,11 @@ class ScatterReduce:
         k_lo = k - k_hi
         L = _lib.lib()
         al = lambda n: -(-n // 256) * 256
-        sizes = [rows * k_lo // 2, L.plq_sf_tiled_bytes(rows, k_lo // 16), rows * k_hi, L.plq_sf_tiled_bytes(rows, k_hi // 32)]
+        # gathered form of the scale bytes: row-major (whole lines per warp over NVLink); each rank re-tiles locally
+        sizes = [rows * k_lo // 2, rows * (k_lo // 16), rows * k_hi, rows * (k_hi // 32)]
+        u8 = dict(dtype=torch.uint8, device=self.device)
+        self.sf_tiled = [(torch.zeros(L.plq_sf_tiled_bytes(rows, k_lo // 16), **u8),
+                          torch.zeros(L.plq_sf_tiled_bytes(rows, k_hi // 32), **u8)) for _ in range(2)]
         self._offsets = [0]
         for n in sizes:
             self._offsets.append(self._offsets[-1] + al(n))
@@ -168,13 +173,16 @@ class ScatterReduce:
         return self.x[self.next, :rows]
 
     def packed(self, which: int, rows: int):
-        """PackedMatrix view of the first `rows` rows of packed-activation set `which`."""
+        """PackedMatrix view of the first `rows` rows of packed-activation set `which` (tiled scale layout: the
+        local re-tiled copy) and the row-major gathered scale buffers behind it."""
         from . import _lib, ops
         k_lo, o, L = self.k - self.k_hi, self._offsets, _lib.lib()
         buf = self.out[which]
-        return ops.PackedMatrix(
+        lo_t, hi_t = self.sf_tiled[which]
+        p = ops.PackedMatrix(
             rows, k_lo, self.k_hi,
             buf[o[0]:o[0] + rows * k_lo // 2].view(rows, k_lo // 2),
-            buf[o[1]:o[1] + L.plq_sf_tiled_bytes(rows, k_lo // 16)],
+            lo_t[:L.plq_sf_tiled_bytes(rows, k_lo // 16)],
             buf[o[2]:o[2] + rows * self.k_hi].view(rows, self.k_hi),
-            buf[o[3]:o[3] + L.plq_sf_tiled_bytes(rows, self.k_hi // 32)], ops.SF_TILED)
+            hi_t[:L.plq_sf_tiled_bytes(rows, self.k_hi // 32)], ops.SF_TILED)
+        return p, buf[o[1]:o[1] + rows * (k_lo // 16)], buf[o[3]:o[3] + rows * (self.k_hi // 32)]

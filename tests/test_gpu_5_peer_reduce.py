@@ -246,10 +246,11 @@ def test_scattered_form_with_emulated_ranks_on_one_gpu(world, total, k, k_hi):
     flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
     sync = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(world)]
     peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
-    outs = [ops.alloc_packed(total, k, k_hi, "tiled", dev) for _ in range(world)]
+    outs = [ops.alloc_packed(total, k, k_hi, "tiled", dev) for _ in range(world)]       # codes + the tiled scales
+    stage = [ops.alloc_packed(total, k, k_hi, "rowmajor", dev) for _ in range(world)]   # gathered row-major scales
     tbl = [0] * 32
-    for r, o in enumerate(outs):
-        for i, t in enumerate((o.lo_codes, o.lo_sf, o.hi_codes, o.hi_sf)):
+    for r in range(world):
+        for i, t in enumerate((outs[r].lo_codes, stage[r].lo_sf, outs[r].hi_codes, stage[r].hi_sf)):
             tbl[8 * i + r] = t.data_ptr()
     tbl_d = torch.tensor(tbl, dtype=torch.int64, device=dev)
     gamma = synth_gamma(k, 3)
@@ -268,9 +269,10 @@ def test_scattered_form_with_emulated_ranks_on_one_gpu(world, total, k, k_hi):
                     flags[r][32 + j] = call
             st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
                 peer_x.data_ptr(), peer_flags.data_ptr(), flags[r].data_ptr(), sync[r].data_ptr(), world, r, -1,
-                tbl_d.data_ptr(), r * per, res_d[r * per:].data_ptr(), h[r * per:].data_ptr(), gamma_d.data_ptr(), 1e-6,
-                per, k, k_hi, 1, outs[r].lo_codes.data_ptr(), outs[r].lo_sf.data_ptr(), outs[r].hi_codes.data_ptr(),
-                outs[r].hi_sf.data_ptr(), 1, ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+                tbl_d.data_ptr(), r * per, total, res_d[r * per:].data_ptr(), h[r * per:].data_ptr(), gamma_d.data_ptr(),
+                1e-6, per, k, k_hi, 1, outs[r].lo_codes.data_ptr(), stage[r].lo_sf.data_ptr(), outs[r].hi_codes.data_ptr(),
+                stage[r].hi_sf.data_ptr(), outs[r].lo_sf.data_ptr(), outs[r].hi_sf.data_ptr(),
+                ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
             assert st == 0
             plq.check_device_status(dev)
             assert int(sync[r][0].item()) == call
@@ -279,10 +281,17 @@ def test_scattered_form_with_emulated_ranks_on_one_gpu(world, total, k, k_hi):
             assert (f[:world] == call).all() and (f[32:32 + world] == call).all()
         want_h, want = _oracle_scatter(parts, res, gamma, k_hi)
         assert np.array_equal(f32_of(h), want_h)
-        for o in outs:
+        # rank r re-tiled the scales at the end of ITS call, when only ranks <= r had run: the last rank's tiled
+        # copy is whole, and so is every rank's gathered row-major form; the codes are whole everywhere
+        for r, o in enumerate(outs):
             got = packed_to_numpy(o)
-            for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
+            for key in ("lo_codes", "hi_codes"):
                 assert np.array_equal(got[key], want[key]), key
+            assert np.array_equal(stage[r].lo_sf.cpu().numpy(), want["lo_sf"])
+            assert np.array_equal(stage[r].hi_sf.cpu().numpy(), want["hi_sf"])
+        # the tiled copy byte for byte, padding (rows and scales beyond the matrix) included
+        assert np.array_equal(outs[world - 1].lo_sf.cpu().numpy(), F.tile_sf(want["lo_sf"]))
+        assert np.array_equal(outs[world - 1].hi_sf.cpu().numpy(), F.tile_sf(want["hi_sf"]))
 
 
 def test_scattered_form_times_out_when_a_peer_never_completes():
@@ -299,7 +308,7 @@ def test_scattered_form_times_out_when_a_peer_never_completes():
     peer_flags = torch.tensor([flags.data_ptr(), other.data_ptr()], dtype=torch.int64, device=dev)
     x = synth_activation(total, k, seed=5).cuda()
     peer_x = torch.tensor([x.data_ptr()] * 2, dtype=torch.int64, device=dev)
-    outs = [ops.alloc_packed(total, k, k_hi, "tiled", dev) for _ in range(2)]
+    outs = [ops.alloc_packed(total, k, k_hi, "rowmajor", dev) for _ in range(2)]
     tbl = [0] * 32
     for r, o in enumerate(outs):
         for i, t in enumerate((o.lo_codes, o.lo_sf, o.hi_codes, o.hi_sf)):
@@ -309,8 +318,8 @@ def test_scattered_form_times_out_when_a_peer_never_completes():
     h = torch.empty(2, k, dtype=torch.bfloat16, device=dev)
     st = _lib.lib().plq_reduce_scatter_add_rmsnorm_pack(
         peer_x.data_ptr(), peer_flags.data_ptr(), flags.data_ptr(), sync.data_ptr(), world, 0, 0, tbl_d.data_ptr(), 0,
-        x.data_ptr(), h.data_ptr(), gamma.data_ptr(), 1e-6, 2, k, k_hi, 1, outs[0].lo_codes.data_ptr(),
-        outs[0].lo_sf.data_ptr(), outs[0].hi_codes.data_ptr(), outs[0].hi_sf.data_ptr(), 1,
+        total, x.data_ptr(), h.data_ptr(), gamma.data_ptr(), 1e-6, 2, k, k_hi, 1, outs[0].lo_codes.data_ptr(),
+        outs[0].lo_sf.data_ptr(), outs[0].hi_codes.data_ptr(), outs[0].hi_sf.data_ptr(), None, None,
         ops.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
     assert st == 0
     with pytest.raises(plq.PlqError) as e:
@@ -347,12 +356,14 @@ def _scatter_worker(rank, world, port, total, k, k_hi, calls, q):
             got = packed_to_numpy(p)
             ok = ok and np.array_equal(f32_of(h), want_h[rank * per:(rank + 1) * per])
             ok = ok and all(np.array_equal(got[key], want[key]) for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"))
-        # the decoder: prefill with the row-sharded residual stream gives the logits of the all-reduce path, bit for bit
+        # the decoder: prefill with the row-sharded residual stream gives, bit for bit, the logits of the path whose
+        # all-reduces run in the all-reduce form of the same kernel (float32 sum in rank order, one rounding; NCCL
+        # rounds its partial sums to bf16 between the ranks, which differs from three ranks on)
         cfg = LlamaConfig(hidden_size=1024, intermediate_size=1024 * world, num_layers=2, num_heads=8 * world,
                           num_kv_heads=world, head_dim=128, vocab_size=512)
         ctx = tp.TPContext(rank, world, None)
         ids = torch.randint(0, cfg.vocab_size, (2, 16 * world), generator=torch.Generator().manual_seed(3)).to(dev)
-        plain = ResQForwardB200(cfg, dev, ctx, seed=5)
+        plain = ResQForwardB200(cfg, dev, ctx, seed=5, fused_reduce_rows=ids.numel())
         a = plain.forward(ids)
         a_all = plain.forward(ids, all_positions=True)
         sharded = ResQForwardB200(cfg, dev, ctx, seed=5, scatter_prefill_rows=ids.numel())
