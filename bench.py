@@ -474,7 +474,8 @@ def main_ours(args, rank, local_rank, world):
 def run_model_tp(args, torch, plq, rank, world, dev, peaks):
     """configs[4] on the ranks of this run: the Llama-3-70B-architecture decoder stack (random init, `--tp-layers`
     of its 80 layers), tensor-parallel over the N ranks (column-parallel QKV / gate_up, row-parallel O / down, one
-    all-reduce per row-parallel linear; decode batches reduce inside the RMSNorm-quant kernel over peer memory),
+    reduction per row-parallel linear, done inside the following RMSNorm-quant kernel over peer memory: all-reduce
+    form for decode batches, reduce-scatter + all-gather of the packed rows for the prefill),
     batch 16, 2048 prefill tokens + 128 greedy decode steps.  Strong scaling: the job is fixed.  Returns the
     `model_tp` block (rank 0) or None."""
     import torch.distributed as dist
@@ -530,7 +531,30 @@ def run_model_tp(args, torch, plq, rank, world, dev, peaks):
             ar[name] = {"bytes_per_allreduce": buf.numel() * 2, "nccl_ms_each": a.elapsed_time(b) / reps,
                         "per_pass": 2 * layers}
             del buf
-        ar["prefill"]["share_of_prefill_ms"] = ar["prefill"]["nccl_ms_each"] * 2 * layers / prefill_ms
+        if scattered:
+            # the kernel that replaces each of those all-reduces AND the add + RMSNorm-quant behind it in the
+            # prefill, timed alone on the model's own buffers (an even number of calls keeps the buffer parity)
+            from plaquant_b200 import ops
+            sr, R = model.scatter, batch * prefill
+            h_my = torch.zeros(R // world, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+            gamma = model.layers[0].ln2
+            for _ in range(2):
+                ops.reduce_scatter_add_rmsnorm_pack(sr, R, h_my, gamma, cfg.rms_eps)
+            sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(4):
+                ops.reduce_scatter_add_rmsnorm_pack(sr, R, h_my, gamma, cfg.rms_eps)
+            b.record()
+            sync()
+            t = torch.tensor([a.elapsed_time(b) / 4], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ar["prefill"]["fused_reduce_scatter_norm_quant_gather_ms_each"] = float(t.item())
+            ar["prefill"]["share_of_prefill_ms"] = float(t.item()) * 2 * layers / prefill_ms
+            ar["prefill"]["note"] = "nccl_ms_each is the all-reduce this run does NOT make, for comparison"
+            del h_my
+        else:
+            ar["prefill"]["share_of_prefill_ms"] = ar["prefill"]["nccl_ms_each"] * 2 * layers / prefill_ms
     # bytes one decode step must read on a rank: packed weights of the linears (tiled copy), the unquantised LM
     # head, and the key/value caches up to the current position (mean over the decode steps)
     w_bytes = sum(lin._gemm_w.nbytes() for L in model.layers for lin in (L.qkv, L.o, L.gate_up, L.down))

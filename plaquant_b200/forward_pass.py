@@ -382,12 +382,7 @@ class ResQForwardB200:
             full = torch.empty(R, c.hidden_size, dtype=h.dtype, device=h.device)
             dist.all_gather_into_tensor(full, h, group=self.ctx.group)
             return self._logits(full.view(b, t, -1))
-        # only the last position of every sequence is needed: its owner contributes it, the others zeros
-        rows = torch.arange(b, device=h.device) * t + (t - 1) - self.ctx.rank * per
-        own = (rows >= 0) & (rows < per)
-        last = torch.where(own[:, None], h[rows.clamp(0, per - 1)].float(), torch.zeros((), device=h.device))
-        dist.all_reduce(last, group=self.ctx.group)            # one non-zero term per row: exact
-        return self._logits(last.to(h.dtype))
+        return self._logits(gather_last_positions(h, b, t, self.ctx.rank, self.ctx.size, self.ctx.group))
 
     def _logits(self, h_last: torch.Tensor) -> torch.Tensor:
         """Final norm + unquantised LM head in the model dtype, for rows [..., hidden] (inference/forward_pass.py:178-181 in the reference)."""
@@ -469,6 +464,20 @@ class ResQForwardB200:
         self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. capture) = ev[1] -> ev[2], once synchronised
         self.pos = t_max
         return out
+
+
+def gather_last_positions(h_slice: torch.Tensor, batch: int, seq: int, rank: int, world: int, group=None) -> torch.Tensor:
+    """Row-sharded residual stream -> the last position of every sequence, on every rank.  `h_slice` holds rows
+    [rank * R / world, (rank + 1) * R / world) of the flattened [batch * seq, hidden] stream; row b * seq + seq - 1
+    is contributed by the rank that owns it and as zeros by the others, and one all-reduce (exact: a single
+    non-zero term per row) hands it to everybody.  Returns [batch, hidden] in the dtype of `h_slice`."""
+    import torch.distributed as dist
+    per = batch * seq // world
+    rows = torch.arange(batch, device=h_slice.device) * seq + (seq - 1) - rank * per
+    own = (rows >= 0) & (rows < per)
+    last = torch.where(own[:, None], h_slice[rows.clamp(0, per - 1)].float(), torch.zeros((), device=h_slice.device))
+    dist.all_reduce(last, group=group)
+    return last.to(h_slice.dtype)
 
 
 class IndependentResQForward:

@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 
 from oracle import formats as F
 from plaquant_b200 import tp
-from tests._util import bits_of, synth_activation, synth_weight
+from tests._util import bits_of, synth_activation, synth_gamma, synth_weight
 
 
 def test_outlier_count_respects_kernel_granularity():
@@ -144,3 +144,66 @@ def test_shards_of_a_weights_dict_partition_the_model():
     x = torch.randn(5, 512, generator=g)
     part = sum(x[:, tp.row_parallel_cols(512, r, 2)] @ f(shards[r]["down"]).T for r in range(2))
     assert torch.allclose(part, x @ bf(full["l0.mlp.down_proj.weight"]).T, atol=1e-4)
+
+
+def _scatter_worker(rank, size, port, out):
+    """The scattered reduction's data flow with gloo standing for the peer loads and stores: every rank sums ITS
+    rows of the partial outputs (float32, rank order, one rounding), adds its slice of the residual stream,
+    normalises / rotates / quantises them with the oracle, and the packed rows are all-gathered."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=size)
+    try:
+        from plaquant_b200.forward_pass import gather_last_positions
+        batch, seq, k, k_hi = 3, 4, 256, 32
+        total = batch * seq
+        per = total // size
+        mine = slice(rank * per, (rank + 1) * per)
+        parts = [synth_activation(total, k, seed=70 + r) for r in range(size)]      # every rank's partial output
+        res = synth_activation(total, k, seed=80)
+        gamma = synth_gamma(k, 81)
+        got = [torch.empty_like(parts[rank]) for _ in range(size)]
+        dist.all_gather(got, parts[rank])                                           # stands for the peer loads
+        acc = np.zeros((per, k), np.float32)
+        for g_ in got:
+            acc = acc + _f32(g_)[mine]
+        h = F.add_bf16(_f32(res)[mine], F.round_to_bf16(acc))
+        p = F.prepare_activation(h, k_hi, gamma=_f32(gamma), eps=1e-6, hadamard=True)
+        gathered = {}
+        for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):                      # stands for the peer stores
+            t = torch.from_numpy(np.ascontiguousarray(p[key]))
+            parts_k = [torch.empty_like(t) for _ in range(size)]
+            dist.all_gather(parts_k, t)
+            gathered[key] = torch.cat(parts_k, 0).numpy()
+        last = gather_last_positions(torch.from_numpy(h).to(torch.bfloat16), batch, seq, rank, size)
+        hs = [torch.empty(per, k) for _ in range(size)]
+        dist.all_gather(hs, torch.from_numpy(h))
+        if rank == size - 1:
+            out.put((gathered, torch.cat(hs, 0).numpy(), last.float().numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_scattered_reduction_on_two_gloo_ranks_equals_the_all_reduce_path():
+    """Reduce-scatter + add + norm + quantise per row slice + all-gather of the packed rows gives the bytes of
+    all-reduce + add + norm + quantise of all rows; the last-position gather returns the right rows."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_scatter_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    gathered, h_all, last = out.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    batch, seq, k, k_hi = 3, 4, 256, 32
+    parts = [synth_activation(batch * seq, k, seed=70 + r) for r in range(2)]
+    acc = _f32(parts[0]) + _f32(parts[1])
+    want_h = F.add_bf16(_f32(synth_activation(batch * seq, k, seed=80)), F.round_to_bf16(acc))
+    want = F.prepare_activation(want_h, k_hi, gamma=_f32(synth_gamma(k, 81)), eps=1e-6, hadamard=True)
+    assert np.array_equal(h_all, want_h)
+    for key in ("lo_codes", "lo_sf", "hi_codes", "hi_sf"):
+        assert np.array_equal(gathered[key], want[key]), key
+    assert np.array_equal(last, want_h.reshape(batch, seq, k)[:, -1])
