@@ -54,6 +54,7 @@ extern "C" {
 #define PLQ_ERR_LIMIT      -7   /* size beyond a documented maximum */
 #define PLQ_DEV_TIMEOUT     1   /* written by a kernel: a bounded wait ran out */
 #define PLQ_DEV_PROTOCOL    2   /* written by a kernel: a fused reduction was called on the wrong buffer set */
+#define PLQ_DEV_RANGE       3   /* written by a kernel: a cache position read from device memory was out of range */
 
 #define PLQ_SF_ROWMAJOR 0
 #define PLQ_SF_TILED    1
@@ -184,6 +185,26 @@ PLQ_API int plq_reduce_scatter_add_rmsnorm_pack(const void* const* peer_x_dev, v
                                                 void* lo_codes, void* lo_sf_rowmajor, void* hi_codes,
                                                 void* hi_sf_rowmajor, void* lo_sf_tiled, void* hi_sf_tiled,
                                                 int32_t* dev_status, void* stream);
+
+/*
+ * Rotary position embedding of the query and key heads of a fused QKV projection and the append of keys and values
+ * to the cache, one pass.  qkv: bf16 [batch * t, ld], each row [heads | kv_heads | kv_heads] x head_dim (128);
+ * cos, sin: float32 [t, 128], row i for the i-th new position.  Per head, x1 = first half, x2 = second half, every
+ * operation rounded to float32 on its own, one rounding to bf16:
+ *     out[i] = x1[i] * cos[i] - x2[i] * sin[i],   out[64 + i] = x2[i] * cos[64 + i] + x1[i] * sin[64 + i].
+ * Outputs: q_out bf16 [batch * t, heads, 128]; rotated keys and unchanged values go to k_cache / v_cache, bf16
+ * [batch, t_max, kv_heads, 128], at positions pos .. pos + t - 1, where pos is read from `pos_dev` (a device
+ * scalar, so that a decode step replayed from a CUDA graph appends at the current position) or, with pos_dev
+ * NULL, is the argument `pos`.  A position outside [0, t_max) read from device memory stores nothing and writes
+ * PLQ_DEV_RANGE to `dev_status`.
+ * Replaces apply_rotary_pos_emb and the cache update of the reference's decoder layer
+ * (inference/forward_pass.py:82-110, 216-247), which run as a dozen PyTorch kernels; the arithmetic is that of
+ * `x.float() * cos + rotate_half(x).float() * sin` rounded to bf16.
+ */
+PLQ_API int plq_rope_kv_append(const void* qkv_bf16, int64_t ld, const void* cos_f32, const void* sin_f32,
+                               int64_t batch, int64_t t, int64_t heads, int64_t kv_heads, int64_t head_dim,
+                               void* q_out_bf16, void* k_cache_bf16, void* v_cache_bf16, int64_t t_max,
+                               const int64_t* pos_dev, int64_t pos, int32_t* dev_status, void* stream);
 
 /*
  * One column block of GPTQ for the block-scaled formats: columns [col0, col0 + count), count <= 128, of the

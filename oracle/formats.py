@@ -370,3 +370,16 @@ def silu_mul_bf16(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     with np.errstate(over="ignore"):
         s = round_to_bf16(g / (F32(1.0) + exp_det(-g)))
     return round_to_bf16(s * np.asarray(up, dtype=F32))
+
+
+def rope_bf16(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """Rotary position embedding of bf16-valued heads, float32 [..., T, heads, D] with cos / sin float32 [T, D]:
+    x * cos + rotate_half(x) * sin with rotate_half(x) = [-x2 | x1], every product and the sum rounded to float32
+    on its own, one rounding to bf16 (inference/forward_pass.py:100-109 in the reference; computed there in the
+    model dtype, here in float32 like the CUDA kernel and the PyTorch formulation it replaces)."""
+    x = x.astype(np.float32)
+    d = x.shape[-1]
+    rot = np.concatenate([-x[..., d // 2:], x[..., :d // 2]], axis=-1)
+    c = cos.astype(np.float32)[:, None, :]
+    s_ = sin.astype(np.float32)[:, None, :]
+    return round_to_bf16((x * c).astype(np.float32) + (rot * s_).astype(np.float32))

@@ -30,6 +30,7 @@ SIGNATURES = {
                                               _vp, _vp, _vp, _vp, _i32, _vp, _vp]),
     "plq_reduce_scatter_add_rmsnorm_pack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp, _vp, _vp, _f32, _i64,
                                                    _i64, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "plq_rope_kv_append": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "plq_gptq_block_frozen": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "plq_gemv_tc": (_i32, [_vp] * 8 + [_i64] * 4 + [_vp, _i64, _vp, _i32, _vp]),
 }

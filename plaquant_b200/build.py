@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libplq_b200.so")
-SOURCES = ["plq_api.cu", "plq_pack.cu", "plq_gemv.cu", "plq_gemv_tc.cu", "plq_gemm.cu", "plq_gptq.cu"]
+SOURCES = ["plq_api.cu", "plq_pack.cu", "plq_gemv.cu", "plq_gemv_tc.cu", "plq_gemm.cu", "plq_gptq.cu", "plq_rope.cu"]
 HEADERS = ["plq_common.cuh", "plq_quant.cuh", "plq_tc.cuh", os.path.join("..", "..", "include", "plq.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -50,6 +50,7 @@ extern "C" const char* plq_status_string(int status) {
     case PLQ_ERR_LIMIT: return "a size exceeds a documented maximum";
     case PLQ_DEV_TIMEOUT: return "a bounded wait inside a kernel ran out; the output is undefined";
     case PLQ_DEV_PROTOCOL: return "a fused reduction was called on the wrong one of its two buffer sets (calls must alternate; a replayed CUDA graph must hold an even number of them); the output is undefined";
+    case PLQ_DEV_RANGE: return "a cache position read from device memory was outside the cache; nothing was stored for it";
     default: return "unknown status";
   }
 }

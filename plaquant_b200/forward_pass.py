@@ -71,6 +71,12 @@ class LlamaConfig:
 _IN_PEER_BUFFER = object()      # marker: a layer's MLP output is waiting, unreduced, in the peer buffer
 
 
+class _DecodeState:
+    """What generate() keeps per (batch, prompt length, steps): static caches, position / mask / token buffers and
+    the captured CUDA graph of one decode step."""
+    __slots__ = ("st", "tok", "out", "step_idx", "arange", "graph", "first_set")
+
+
 class _Layer:
     __slots__ = ("ln1", "ln2", "qkv", "o", "gate_up", "down")
 
@@ -119,6 +125,7 @@ class ResQForwardB200:
                 self.lm_head = (torch.randn(c.vocab_size, c.hidden_size, generator=g, device=self.device) * 0.02).to(torch.bfloat16)
         self.kv: List[Tuple[torch.Tensor, torch.Tensor]] = []
         self.pos = 0
+        self._decode_states: Dict[tuple, _DecodeState] = {}
         # keys go into the cache as NVFP4 (Hadamard over the head dimension, per-head rows), queries get the same
         # rotation: the reference's QKRotationWrapper with k_had (promix/quantize/kv_quant.py:244-279)
         self.kv_quant = kv_quant                     # False | True (packed NVFP4 rows in the cache) | "fake" (their bf16 values)
@@ -250,6 +257,26 @@ class ResQForwardB200:
         cache -> [B, T, heads * head_dim] (this rank's heads)."""
         c = self.cfg
         b, t, _ = qkv.shape
+        if not self.kv_quant and c.head_dim == 128:
+            # RoPE on q and k and the cache append in one kernel (same float32 arithmetic as _rope, bit for bit)
+            cos, sin = cos_sin[0].reshape(t, c.head_dim), cos_sin[1].reshape(t, c.head_dim)
+            if static is None:
+                k = torch.empty(b, t, self.kv_heads, c.head_dim, dtype=qkv.dtype, device=qkv.device)
+                v = torch.empty_like(k)
+                q = ops.rope_kv_append(qkv, cos, sin, self.heads, self.kv_heads, k, v, 0)
+                if pos0 == 0:
+                    self.kv[li] = (k, v)
+                else:
+                    self.kv[li] = (torch.cat([self.kv[li][0], k], 1), torch.cat([self.kv[li][1], v], 1))
+                kk, vv = self.kv[li]
+                attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                      is_causal=(t > 1), enable_gqa=True)
+            else:
+                kk, vv = static["k"][li], static["v"][li]
+                q = ops.rope_kv_append(qkv, cos, sin, self.heads, self.kv_heads, kk, vv, static["pos"])
+                attn = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                      attn_mask=static["mask"], enable_gqa=True)
+            return attn.transpose(1, 2).reshape(b, t, self.heads * c.head_dim)
         q, k, v = qkv.split([self.heads * c.head_dim, self.kv_heads * c.head_dim, self.kv_heads * c.head_dim], -1)
         q, k, v = q.view(b, t, self.heads, c.head_dim), k.view(b, t, self.kv_heads, c.head_dim), v.view(b, t, self.kv_heads, c.head_dim)
         q, k = self._rope(q, k, cos_sin)
@@ -395,7 +422,8 @@ class ResQForwardB200:
 
         With `use_graph` the decode step (fixed shapes: caches preallocated for prefill + steps positions, the
         position and the attention mask held in device memory) is captured once in a CUDA graph and replayed, so
-        a step costs its kernels and not ~2000 Python-side launches."""
+        a step costs its kernels and not ~2000 Python-side launches.  The graph and its buffers are kept: the next
+        call with the same batch, prompt length and step count reloads the caches and replays every step."""
         if not use_graph or steps < 2:
             out = []
             nxt = self.forward(input_ids).argmax(-1, keepdim=True)
@@ -411,22 +439,35 @@ class ResQForwardB200:
         ev[0].record()
         nxt = self.forward(input_ids).argmax(-1, keepdim=True)              # eager prefill fills self.kv
         ev[1].record()
-        st = {"k": [], "v": [], "pos": torch.full((1,), t0, dtype=torch.int64, device=dev),
-              "mask": torch.zeros(1, 1, 1, t_max, dtype=torch.bool, device=dev)}
+        # the decode state of this shape - caches, position, mask, token buffers and, once captured, the graph - is
+        # kept: a later call with the same (batch, prompt length, steps) reloads the caches and only replays
+        S = self._decode_states.get((b, t0, steps))
+        if S is None:
+            S = _DecodeState()
+            S.st = {"k": [], "v": [], "pos": torch.zeros(1, dtype=torch.int64, device=dev),
+                    "mask": torch.zeros(1, 1, 1, t_max, dtype=torch.bool, device=dev)}
+            for li in range(len(self.layers)):
+                for name, src in (("k", self.kv[li][0]), ("v", self.kv[li][1])):    # bf16 rows or packed rows
+                    S.st[name].append(torch.zeros(b, t_max, self.kv_heads, src.shape[-1], dtype=src.dtype, device=dev))
+            S.tok = torch.zeros_like(nxt)                                    # [B, 1] current token, updated in place
+            S.out = torch.zeros(b, steps, dtype=nxt.dtype, device=dev)
+            S.step_idx = torch.zeros(1, dtype=torch.int64, device=dev)
+            S.arange = torch.arange(t_max, device=dev)
+            S.graph, S.first_set = None, None
+            self._decode_states.clear()                                      # one shape at a time: the caches are large
+            self._decode_states[(b, t0, steps)] = S
+        st, tok, out, step_idx = S.st, S.tok, S.out, S.step_idx
         for li in range(len(self.layers)):
-            for name, src in (("k", self.kv[li][0]), ("v", self.kv[li][1])):
-                buf = torch.zeros(b, t_max, self.kv_heads, src.shape[-1], dtype=src.dtype, device=dev)   # bf16 rows or packed rows
-                buf[:, :t0] = src
-                st[name].append(buf)
+            st["k"][li][:, :t0].copy_(self.kv[li][0])
+            st["v"][li][:, :t0].copy_(self.kv[li][1])
         self.kv = [None] * len(self.layers)
-        tok = nxt.clone()                                                    # [B, 1] current token, updated in place
-        out = torch.zeros(b, steps, dtype=nxt.dtype, device=dev)
-        step_idx = torch.zeros(1, dtype=torch.int64, device=dev)
-        arange = torch.arange(t_max, device=dev)
+        st["pos"].fill_(t0)
+        step_idx.zero_()
+        tok.copy_(nxt)
 
         def decode_step():
             out.index_copy_(1, step_idx, tok)
-            st["mask"].copy_((arange <= st["pos"]).view(1, 1, 1, t_max))
+            st["mask"].copy_((S.arange <= st["pos"]).view(1, 1, 1, t_max))
             h = F.embedding(tok, self.embed)
             cos_sin = self._rope_angles(st["pos"].to(torch.float32))
             delta = None
@@ -436,8 +477,11 @@ class ResQForwardB200:
             st["pos"].add_(1)
             step_idx.add_(1)
 
-        decode_step()                                                        # warm-up (also step 0 of the output)
-        if steps > 1:
+        if S.graph is not None and (self.peer is None or self.peer.next == S.first_set):
+            for _ in range(steps):                                           # every step from the kept graph
+                S.graph.replay()
+        else:
+            decode_step()                                                    # warm-up (also step 0 of the output)
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(torch.cuda.current_stream(dev))
             graph = torch.cuda.CUDAGraph()
@@ -446,6 +490,7 @@ class ResQForwardB200:
                 side.synchronize()
                 if steps > 2:
                     calls_before = self.peer.calls if self.peer is not None else 0
+                    S.first_set = self.peer.next if self.peer is not None else None
                     with torch.cuda.graph(graph, stream=side):
                         decode_step()
             torch.cuda.current_stream(dev).wait_stream(side)
@@ -459,11 +504,13 @@ class ResQForwardB200:
                 dist.barrier(self.ctx.group)
             for _ in range(steps - 2):                                       # capture does not execute: steps 2 .. steps-1
                 graph.replay()
+            if steps > 2:
+                S.graph = graph
         ev[2].record()
         ops.check_device_status(dev)                                         # a missing rank or a protocol error is loud
-        self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. capture) = ev[1] -> ev[2], once synchronised
+        self.timing_events = ev      # prefill = ev[0] -> ev[1], decode (incl. a capture, if any) = ev[1] -> ev[2], once synchronised
         self.pos = t_max
-        return out
+        return out.clone()           # the buffer belongs to the kept decode state
 
 
 def gather_last_positions(h_slice: torch.Tensor, batch: int, seq: int, rank: int, world: int, group=None) -> torch.Tensor:

@@ -219,6 +219,36 @@ def reduce_scatter_add_rmsnorm_pack(sr, rows_total: int, residual: torch.Tensor,
     return h, p
 
 
+def rope_kv_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, heads: int, kv_heads: int,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, pos) -> torch.Tensor:
+    """RoPE on the query and key heads of `qkv` (bf16 [B, T, (heads + 2 kv_heads) * 128]) and append of the rotated
+    keys and the values to `k_cache` / `v_cache` (bf16 [B, T_max, kv_heads, 128]) at positions pos .. pos + T - 1, one
+    kernel.  `cos` / `sin`: float32 with T * 128 elements (one row per new position).  `pos`: an int, or a device
+    int64 tensor with one element (read by the kernel: a captured decode step appends at the current position).
+    Returns the rotated queries, bf16 [B, T, heads, 128]."""
+    _require_cuda(qkv, "qkv")
+    b, t, n = qkv.shape
+    if qkv.dtype != torch.bfloat16 or not qkv.is_contiguous() or n != (heads + 2 * kv_heads) * 128:
+        raise TypeError("qkv must be contiguous bfloat16 [B, T, (heads + 2 kv_heads) * 128]")
+    for name, c in (("cos", cos), ("sin", sin)):
+        if c.dtype != torch.float32 or c.numel() != t * 128 or not c.is_contiguous():
+            raise TypeError(f"{name} must be contiguous float32 with T * 128 elements")
+    t_max = k_cache.shape[1]
+    for name, c in (("k_cache", k_cache), ("v_cache", v_cache)):
+        if c.dtype != torch.bfloat16 or not c.is_contiguous() or tuple(c.shape) != (b, t_max, kv_heads, 128):
+            raise TypeError(f"{name} must be contiguous bfloat16 [B, T_max, kv_heads, 128]")
+    on_device = isinstance(pos, torch.Tensor)
+    if on_device and (pos.dtype != torch.int64 or pos.numel() != 1 or pos.device != qkv.device):
+        raise TypeError("pos must be an int or a one-element int64 tensor on the device of qkv")
+    q = torch.empty(b, t, heads, 128, dtype=torch.bfloat16, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        st = _lib.lib().plq_rope_kv_append(_ptr(qkv), n, _ptr(cos), _ptr(sin), b, t, heads, kv_heads, 128, _ptr(q),
+                                           _ptr(k_cache), _ptr(v_cache), t_max, _ptr(pos) if on_device else None,
+                                           0 if on_device else int(pos), _ptr(status_word(qkv.device)), _stream(qkv.device))
+    _lib.check(st)
+    return q
+
+
 def unpack(p: PackedMatrix) -> torch.Tensor:
     """Dequantise to bf16 [rows, K]: the value the reference's fake quantiser returns."""
     y = torch.empty(p.rows, p.k, dtype=torch.bfloat16, device=p.device)

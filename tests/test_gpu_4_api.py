@@ -220,3 +220,29 @@ def test_independent_resq_forward_from_a_weights_dict_matches_the_seeded_decoder
     with pytest.raises(ValueError):
         weight_packer.load_packed(path, "cuda", ctx=tp.TPContext(1, 2, None))   # written for one rank, not for rank 1 of 2
     plq.check_device_status()
+
+
+def test_generate_keeps_its_decode_graph_between_calls():
+    """The second generate() with the same batch, prompt length and step count replays the kept graph for every
+    step: same tokens as the first call and as the eager loop, also for a different prompt of that shape; another
+    shape builds a new state."""
+    from plaquant_b200.forward_pass import LlamaConfig, ResQForwardB200
+    cfg = LlamaConfig(hidden_size=1024, intermediate_size=2048, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=128,
+                      vocab_size=512)
+    g = torch.Generator().manual_seed(21)
+    ids_a = torch.randint(0, cfg.vocab_size, (3, 20), generator=g).cuda()
+    ids_b = torch.randint(0, cfg.vocab_size, (3, 20), generator=g).cuda()
+    m = ResQForwardB200(cfg, "cuda", seed=2)
+    eager_a = m.generate(ids_a, 7, use_graph=False)
+    eager_b = m.generate(ids_b, 7, use_graph=False)
+    first = m.generate(ids_a, 7)
+    state = m._decode_states[(3, 20, 7)]
+    assert state.graph is not None
+    assert torch.equal(first, eager_a)
+    assert torch.equal(m.generate(ids_a, 7), eager_a) and m._decode_states[(3, 20, 7)] is state
+    assert torch.equal(m.generate(ids_b, 7), eager_b)
+    assert torch.equal(m.generate(ids_a, 7), eager_a)
+    shorter = m.generate(ids_a[:, :12], 7)
+    assert (3, 12, 7) in m._decode_states and (3, 20, 7) not in m._decode_states
+    assert torch.equal(shorter, m.generate(ids_a[:, :12], 7, use_graph=False))
+    plq.check_device_status()

@@ -157,3 +157,20 @@ def test_reference_quantiser_staged_for_the_benchmark_agrees_with_the_oracle():
     got = q(x).float().numpy()
     xf = F.bf16_bits_to_f32(x.view(torch.int16).numpy().view(np.uint16))
     assert np.array_equal(got, F.round_to_bf16(F.dequant_mixed(F.pack_mixed(xf, 64))))
+
+
+def test_rope_oracle_equals_the_pytorch_formulation():
+    """`rope_bf16` against `x.float() * cos + rotate_half(x).float() * sin` rounded to bf16, computed by PyTorch on
+    the CPU (the formulation of apply_rotary_pos_emb, inference/forward_pass.py:100-109 in the reference, in
+    float32), on every position of a 300-token window and bf16 inputs of mixed magnitude."""
+    import torch
+    g = torch.Generator().manual_seed(12)
+    t, heads = 300, 3
+    x = (torch.randn(2, t, heads, 128, generator=g) * torch.logspace(-3, 2, heads)[None, None, :, None]).to(torch.bfloat16)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    ang = torch.outer(torch.arange(t, dtype=torch.float32), inv)
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+    x1, x2 = x[..., :64], x[..., 64:]
+    want = (x.float() * cos[None, :, None, :] + torch.cat([-x2, x1], -1).float() * sin[None, :, None, :]).to(torch.bfloat16)
+    got = F.rope_bf16(x.float().numpy(), cos.numpy(), sin.numpy())
+    assert np.array_equal(got, want.float().numpy())
