@@ -319,7 +319,7 @@ class ResQForwardB200:
 
         Without `static`, keys and values are kept in a growing Python-side cache (prefill, and decode steps of
         arbitrary length).  With `static` (a dict holding preallocated caches [B, T_max, ...], the device tensors
-        `pos` [1] int64 and `mask` [1, 1, 1, T_max] bool) every shape is fixed and the position is data, which
+        `pos` [1] int64 and the additive `mask` [1, 1, 1, T_max]) every shape is fixed and the position is data, which
         is what CUDA-graph capture of a decode step needs."""
         c, L = self.cfg, self.layers[li]
         b, t, _ = h.shape
@@ -442,10 +442,11 @@ class ResQForwardB200:
         # the decode state of this shape - caches, position, mask, token buffers and, once captured, the graph - is
         # kept: a later call with the same (batch, prompt length, steps) reloads the caches and only replays
         S = self._decode_states.get((b, t0, steps))
+        nxt_dtype = self.embed.dtype       # the attention mask is additive, in the model dtype, built once per step
         if S is None:
             S = _DecodeState()
             S.st = {"k": [], "v": [], "pos": torch.zeros(1, dtype=torch.int64, device=dev),
-                    "mask": torch.zeros(1, 1, 1, t_max, dtype=torch.bool, device=dev)}
+                    "mask": torch.zeros(1, 1, 1, t_max, dtype=nxt_dtype, device=dev)}      # additive: 0 / -inf
             for li in range(len(self.layers)):
                 for name, src in (("k", self.kv[li][0]), ("v", self.kv[li][1])):    # bf16 rows or packed rows
                     S.st[name].append(torch.zeros(b, t_max, self.kv_heads, src.shape[-1], dtype=src.dtype, device=dev))
@@ -467,7 +468,7 @@ class ResQForwardB200:
 
         def decode_step():
             out.index_copy_(1, step_idx, tok)
-            st["mask"].copy_((S.arange <= st["pos"]).view(1, 1, 1, t_max))
+            st["mask"].copy_(torch.where(S.arange <= st["pos"], 0.0, float("-inf")).view(1, 1, 1, t_max))
             h = F.embedding(tok, self.embed)
             cos_sin = self._rope_angles(st["pos"].to(torch.float32))
             delta = None

@@ -80,8 +80,12 @@ def alloc_packed(rows: int, k: int, k_hi: int, sf_layout, device) -> PackedMatri
     L = _lib.lib()
     u8 = dict(dtype=torch.uint8, device=device)
     if layout == SF_TILED:
-        lo_sf = torch.zeros(L.plq_sf_tiled_bytes(rows, k_lo // 16), **u8)
-        hi_sf = torch.zeros(L.plq_sf_tiled_bytes(rows, k_hi // 32), **u8)
+        # Padding.  Rows beyond `rows` inside the last 128-row group only ever scale output rows that are not stored,
+        # so they may hold anything.  Scales beyond K inside the last chunk of four meet zero codes in an MMA, and
+        # 0 x NaN is NaN: they must be zero.  K_lo / 16 is always a multiple of four; K_hi / 32 need not be.
+        lo_sf = torch.empty(L.plq_sf_tiled_bytes(rows, k_lo // 16), **u8)
+        hi_bytes = L.plq_sf_tiled_bytes(rows, k_hi // 32)
+        hi_sf = torch.zeros(hi_bytes, **u8) if (k_hi // 32) % 4 else torch.empty(hi_bytes, **u8)
     else:
         lo_sf = torch.empty(rows, k_lo // 16, **u8)
         hi_sf = torch.empty(rows, k_hi // 32, **u8)
