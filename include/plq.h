@@ -22,7 +22,11 @@
  *   PLQ_SF_TILED     512-byte chunks of 128 rows x 4 scales, byte (r%32)*16 + (r%128)/32*4
  *                    + (k%4), chunks ordered K-fastest, rows and scales padded to 128 and 4:
  *                    the order a block-scaled tcgen05.mma reads from tensor memory.
- *                    Size in bytes: plq_sf_tiled_bytes(rows, n_scales_per_row).
+ *                    Size in bytes: plq_sf_tiled_bytes(rows, n_scales_per_row).  The pack kernels
+ *                    write only the real entries.  Padding scales beyond the row's last one (inside
+ *                    its last chunk of four) must be zero: the MMA multiplies them with zero codes,
+ *                    and 0 x NaN is NaN.  Padding rows may hold anything: they only scale output rows
+ *                    that are never stored.
  * Constraints: K_lo % 64 == 0, K_hi % 32 == 0, K % 128 == 0 when a Hadamard rotation or
  * RMSNorm is requested, K <= 32768; all pointers 16-byte aligned.
  *
