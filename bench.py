@@ -789,6 +789,18 @@ def main_case(args):
         pa = plq.alloc_packed(args.m, f, f // 32, "tiled", dev)
         fn = lambda: plq.silu_mul_pack(gu, f // 32, out=pa)
         work, unit = args.m * (2 * f * 2 + pa.nbytes() // args.m), "GB/s"
+    elif args.case == "rope":
+        # the fused QKV output of one Llama-3-70B layer, `m` token rows of 4 sequences: RoPE on q / k, append of k / v
+        from plaquant_b200 import ops
+        heads, kvh, b = 64, 8, 4
+        t = args.m // b
+        qkv = activ(args.m, (heads + 2 * kvh) * 128).view(b, t, -1)
+        ang = torch.outer(torch.arange(t, dtype=torch.float32), 1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128)))
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1).to(dev), torch.cat([ang.sin(), ang.sin()], -1).to(dev)
+        kc = torch.empty(b, t, kvh, 128, dtype=torch.bfloat16, device=dev)
+        vc = torch.empty_like(kc)
+        fn = lambda: ops.rope_kv_append(qkv, cos, sin, heads, kvh, kc, vc, 0)
+        work, unit = 2 * qkv.numel() * 2, "GB/s"
     elif args.case in ("gemv", "gemv_tc"):
         layout, op = (("rowmajor", plq.gemv) if args.case == "gemv" else
                       ("tiled", lambda a_, b_, out: plq.gemv_tc(a_, b_, out=out, static_weights=True)))
@@ -828,7 +840,7 @@ def main_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default=None, choices=["pack", "silu_pack", "gemv", "gemv_tc", "gemm", "decode_step"],
+    ap.add_argument("--case", default=None, choices=["pack", "silu_pack", "rope", "gemv", "gemv_tc", "gemm", "decode_step"],
                     help="run one kernel on one fixed case instead of the full step")
     ap.add_argument("--shape", default="qkv", choices=[s[0] for s in SHAPES])
     ap.add_argument("--m", type=int, default=None)

@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-__global__ void __launch_bounds__(256) rope_kv_append_kernel(const RopeArgs a) {
+__global__ void __launch_bounds__(256, 6) rope_kv_append_kernel(const RopeArgs a) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= a.total) return;
   const int all_heads = a.heads + 2 * a.kv_heads;
