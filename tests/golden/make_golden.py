@@ -14,6 +14,7 @@ What is stored (all small, deterministic, seeded):
   kats.npz ............... tie / midpoint / zero / saturation known answers.
   norm_rot.npz ........... rms_norm -> (x.float() @ H).to(bf16) from the reference functions,
                            used to bound the deterministic restatement's distance from torch.
+  rope.npz ............... apply_rotary_pos_emb of the reference on bf16-valued float32 heads.
   linear_cfg0.npz ........ the single-linear config: Y = F.linear(fq(rot(X)), fq(rot(W))) in
                            bf16 and the same product in float32, with input checksums.
 """
@@ -206,6 +207,21 @@ def main(ref_root):
     Qg = layer.weight.data.float()
     np.savez_compressed(os.path.join(HERE, "gptq_frozen.npz"), w=bf16_bits(Wg), hinv=Hinv.numpy(), q=Qg.numpy(),
                         k_hi=np.int64(k_hi))
+    # ---------------- rope -------------------------------------------------------------------
+    # The reference's apply_rotary_pos_emb (inference/forward_pass.py:82-116) on bf16-valued float32 heads with
+    # float32 tables (the reference's decoder feeds it the model dtype; the formula is the same): the product of
+    # this repository's kernel is its result rounded to bf16.
+    g = torch.Generator().manual_seed(13)
+    t, hq, hk = 9, 3, 2
+    qf = (torch.randn(2, t, hq, 128, generator=g) * 3).to(torch.bfloat16)
+    kf = (torch.randn(2, t, hk, 128, generator=g) * 0.3).to(torch.bfloat16)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    emb = torch.outer(torch.arange(37, 37 + t, dtype=torch.float32), inv)
+    emb = torch.cat((emb, emb), dim=-1)
+    cos, sin = emb.cos(), emb.sin()
+    q_out, k_out = fp.apply_rotary_pos_emb(qf.float(), kf.float(), cos, sin)
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), q=bf16_bits(qf), k=bf16_bits(kf), cos=cos.numpy(), sin=sin.numpy(),
+                        q_out=q_out.numpy(), k_out=k_out.numpy())
     print("golden fixtures written to", HERE)
 
 

@@ -174,3 +174,13 @@ def test_rope_oracle_equals_the_pytorch_formulation():
     want = (x.float() * cos[None, :, None, :] + torch.cat([-x2, x1], -1).float() * sin[None, :, None, :]).to(torch.bfloat16)
     got = F.rope_bf16(x.float().numpy(), cos.numpy(), sin.numpy())
     assert np.array_equal(got, want.float().numpy())
+
+
+def test_rope_oracle_against_the_reference_fixture(golden_dir):
+    """`rope_bf16` against apply_rotary_pos_emb of the reference run on the same bf16-valued heads and float32
+    tables (tests/golden/make_golden.py), rounded to bf16: queries and keys, positions 37..45."""
+    g = np.load(os.path.join(golden_dir, "rope.npz"))
+    for name in ("q", "k"):
+        x = F.bf16_bits_to_f32(g[name])
+        got = F.rope_bf16(x, g["cos"], g["sin"])
+        assert np.array_equal(got, F.round_to_bf16(g[name + "_out"])), name
