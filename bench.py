@@ -407,7 +407,10 @@ def main_ours(args, rank, local_rank, world):
             L["pw"] = L["pa"] = L["y"] = None
         x_dev.clear(); x_in.clear()
         torch.cuda.empty_cache()
-        model_tp = run_model_tp(args, torch, plq, rank, world, dev, peaks)
+        try:
+            model_tp = run_model_tp(args, torch, plq, rank, world, dev, peaks)
+        except Exception as exc:  # noqa: BLE001 - the headline line below is still printed, with the failure in it
+            model_tp = {"error": f"{type(exc).__name__}: {exc}"[:400]} if rank == 0 else None
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
