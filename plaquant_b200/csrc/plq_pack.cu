@@ -82,15 +82,18 @@ __device__ __forceinline__ float2 round_bf16_pair(const float2 y) {
   return make_float2(bf16lo_to_f32(b), bf16hi_to_f32(b));
 }
 
-// Output stores.  Plain: this rank's buffer.  Scattered tensor-parallel prologue: the same bytes into the buffer of
-// every rank (an all-gather by peer stores over NVLink).  `which` = 0 lo_codes, 1 lo_sf, 2 hi_codes, 3 hi_sf.
-template <typename T>
+// Output stores.  Plain: this rank's buffer.  Scattered tensor-parallel prologue (PRO 3 with an output table): the
+// same bytes into the buffer of every rank (an all-gather by peer stores over NVLink).  `which` = 0 lo_codes, 1 lo_sf,
+// 2 hi_codes, 3 hi_sf.  Only prologue 3 carries the table: the other kernels compile to the plain store.
+template <int PRO, typename T>
 __device__ __forceinline__ void store_out(const PackArgs& a, int which, uint8_t* own, size_t off, const T& val) {
-  if (a.out_tbl == nullptr) {
-    *reinterpret_cast<T*>(own + off) = val;
-  } else {
-    for (int r = 0; r < a.world; ++r) *reinterpret_cast<T*>(a.out_tbl[8 * which + r] + off) = val;
+  if constexpr (PRO == 3) {
+    if (a.out_tbl != nullptr) {
+      for (int r = 0; r < a.world; ++r) *reinterpret_cast<T*>(a.out_tbl[8 * which + r] + off) = val;
+      return;
+    }
   }
+  *reinterpret_cast<T*>(own + off) = val;
 }
 
 // Quantises one NVFP4 run of 32 elements (sixteen float32 pairs, bf16-valued): its 16 bytes of codes go to `codes`,
@@ -118,11 +121,13 @@ __device__ __forceinline__ uint32_t quantize_run_nvfp4(const float2* v, uint4& c
 }
 
 // Codes of the run that starts at element `o` of output row `row` (o < k_lo).
+template <int PRO>
 __device__ __forceinline__ void store_run_nvfp4(const PackArgs& a, const uint4& codes, int row, int o) {
-  store_out(a, 0, a.lo_codes, (static_cast<size_t>(row) * a.k_lo + o) / 2, codes);
+  store_out<PRO>(a, 0, a.lo_codes, (static_cast<size_t>(row) * a.k_lo + o) / 2, codes);
 }
 
 // The same for a run in the MXFP8 columns (o >= k_lo): 32 code bytes and one scale byte.
+template <int PRO>
 __device__ __forceinline__ void quantize_run_mxfp8(const PackArgs& a, const float2* v, int row, int o) {
   float m0 = 0.0f, m1 = 0.0f;
 #pragma unroll
@@ -136,12 +141,12 @@ __device__ __forceinline__ void quantize_run_mxfp8(const PackArgs& a, const floa
   const uint2 c2 = mxfp8_quantize8(v + 8, inv), c3 = mxfp8_quantize8(v + 12, inv);
   const int k_hi = a.k - a.k_lo, kh = o - a.k_lo;
   const size_t coff = static_cast<size_t>(row) * k_hi + kh;
-  store_out(a, 2, a.hi_codes, coff, make_uint4(c0.x, c0.y, c1.x, c1.y));
-  store_out(a, 2, a.hi_codes, coff + 16, make_uint4(c2.x, c2.y, c3.x, c3.y));
+  store_out<PRO>(a, 2, a.hi_codes, coff, make_uint4(c0.x, c0.y, c1.x, c1.y));
+  store_out<PRO>(a, 2, a.hi_codes, coff + 16, make_uint4(c2.x, c2.y, c3.x, c3.y));
   const int kb = kh >> 5;
   const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(row, kb, a.hi_chunks))
                                 : static_cast<size_t>(row) * (k_hi >> 5) + kb;
-  store_out(a, 3, a.hi_sf, off, static_cast<uint8_t>(c));
+  store_out<PRO>(a, 3, a.hi_sf, off, static_cast<uint8_t>(c));
 }
 
 // ---- staging through shared memory -------------------------------------------------------
@@ -522,15 +527,17 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
     const bool hi0 = o0 >= a.k_lo && o0 < a.k, hi1 = o1 >= a.k_lo && o1 < a.k;
     uint4 c0, c1;
     if (!__any_sync(0xFFFFFFFFu, hi0 || hi1)) {     // the usual case: the whole warp is in the NVFP4 columns
+      bool gather = false;                           // scattered form of prologue 3: stores go to every rank
+      if constexpr (PRO == 3) gather = a.out_tbl != nullptr;
       sf = quantize_run_nvfp4(v, c0);
+      if (!gather && row_ok && o0 < a.k_lo) store_run_nvfp4<PRO>(a, c0, orow, o0);
       sf |= quantize_run_nvfp4(v + 16, c1) << 16;
-      bool direct = true;
+      if (!gather && row_ok && o1 < a.k_lo) store_run_nvfp4<PRO>(a, c1, orow, o1);
       if constexpr (PRO == 3) {
-        if (a.out_tbl != nullptr) {
-          // Scattered form: the warp's 1 KB of codes goes to every rank.  Each lane holds two 16-byte pieces that
-          // are not neighbours of the next lane's; they pass through the warp's (now free) x slot so that one
-          // store instruction covers 512 consecutive bytes - whole lines over NVLink instead of half sectors.
-          direct = false;
+        if (gather) {
+          // The warp's 1 KB of codes goes to every rank.  Each lane holds two 16-byte pieces that are not
+          // neighbours of the next lane's; they pass through the warp's (now free) x slot so that one store
+          // instruction covers 512 consecutive bytes - whole lines over NVLink instead of half sectors.
           uint8_t* sc = xs0 + cur_slot * stage_bytes;
           const int seg0 = 2048 * unit.seg;
           const int q0 = (o0 - seg0) >> 5, q1 = (o1 - seg0) >> 5;           // piece index inside the segment
@@ -550,20 +557,16 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
           __syncwarp();                                // the slot is summed into again only after this
         }
       }
-      if (direct) {
-        if (row_ok && o0 < a.k_lo) store_run_nvfp4(a, c0, orow, o0);
-        if (row_ok && o1 < a.k_lo) store_run_nvfp4(a, c1, orow, o1);
-      }
     } else {                                         // a warp that holds MXFP8 columns
       sf = 0;
       if (o0 < a.k_lo) {
         sf = quantize_run_nvfp4(v, c0);
-        if (row_ok) store_run_nvfp4(a, c0, orow, o0);
-      } else if (hi0 && row_ok) quantize_run_mxfp8(a, v, orow, o0);
+        if (row_ok) store_run_nvfp4<PRO>(a, c0, orow, o0);
+      } else if (hi0 && row_ok) quantize_run_mxfp8<PRO>(a, v, orow, o0);
       if (o1 < a.k_lo) {
         sf |= quantize_run_nvfp4(v + 16, c1) << 16;
-        if (row_ok) store_run_nvfp4(a, c1, orow, o1);
-      } else if (hi1 && row_ok) quantize_run_mxfp8(a, v + 16, orow, o1);
+        if (row_ok) store_run_nvfp4<PRO>(a, c1, orow, o1);
+      } else if (hi1 && row_ok) quantize_run_mxfp8<PRO>(a, v + 16, orow, o1);
     }
     // NVFP4 scale bytes, one 32-bit word per 64 elements.  Plain rows: the lane's own four bytes.  Rotated rows:
     // the even lane has bytes 0,1 of both words of its block and the odd lane bytes 2,3: one exchange, one word each.
@@ -575,7 +578,7 @@ __global__ void PLQ_PACK_BOUNDS pack_kernel(const PackArgs a) {
       const int kb = 4 * l;
       const size_t off = a.sf_tiled ? static_cast<size_t>(sf_tiled_offset(orow, kb, a.lo_chunks))
                                     : static_cast<size_t>(orow) * (a.k_lo >> 4) + kb;
-      store_out(a, 1, a.lo_sf, off, sf);
+      store_out<PRO>(a, 1, a.lo_sf, off, sf);
     }
   }
   cp_async_wait_all();
